@@ -46,6 +46,7 @@ def host_library() -> ctypes.CDLL:
 @dataclass(frozen=True)
 class GroupInfo:
     window: int              # 0 = all keys
+    keep_first: int          # a windowed group keeps the pages of a request's first tokens
     num_pages: int
     layers: Tuple[int, ...]  # cache layers that share this group's block tables
 
@@ -218,22 +219,26 @@ class CacheManager(PageTable):
 
     def __init__(self, specs: Sequence[CacheSpec], dtype: torch.dtype, device, page_size: int,
                  num_pages: int, max_requests: int, max_model_len: int):
-        windows: List[int] = []
+        kinds: List[Tuple[int, int]] = []          # (window, kept first tokens) of each group
         members: List[List[int]] = []
         self.layer_group: List[int] = []
         for i, sp in enumerate(specs):
             if isinstance(sp, PagedKVSpec):
-                if sp.window not in windows:
-                    windows.append(sp.window)
+                kind = (sp.window, sp.keep_first if sp.window > 0 else 0)
+                if kind not in kinds:
+                    kinds.append(kind)
                     members.append([])
-                g = windows.index(sp.window)
+                g = kinds.index(kind)
                 members[g].append(i)
                 self.layer_group.append(g)
             else:
                 self.layer_group.append(-1)
         max_blocks = (max_model_len + page_size - 1) // page_size
-        super().__init__(windows, [num_pages] * len(windows), page_size, max_requests, max_blocks)
-        self.groups = [GroupInfo(w, num_pages, tuple(m)) for w, m in zip(windows, members)]
+        super().__init__([w for w, _ in kinds], [num_pages] * len(kinds), page_size, max_requests, max_blocks)
+        for g, (_, keep) in enumerate(kinds):
+            if keep and self._lib.kcache_set_keep_first(self._h, g, keep) != 0:
+                raise CacheError(f"cache manager: group {g} cannot keep the first {keep} tokens")
+        self.groups = [GroupInfo(w, k, num_pages, tuple(m)) for (w, k), m in zip(kinds, members)]
         self.specs = list(specs)
         self.null_page = num_pages
         self.spare_slot = max_requests
@@ -247,7 +252,7 @@ class CacheManager(PageTable):
                 # of a captured step write their keys and values
                 shape = (num_pages + 1, sp.kv_heads, page_size, sp.head_dim)
                 self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-                self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+                self.v.append(torch.zeros(shape[:3] + (sp.value_dim,), dtype=dtype, device=device))
                 self.state.append(None)
             elif isinstance(sp, FixedStateSpec):
                 self.k.append(None)
@@ -286,5 +291,5 @@ class CacheManager(PageTable):
         n = 0
         for sp in self.specs:
             if isinstance(sp, PagedKVSpec):
-                n += 2 * sp.kv_heads * sp.head_dim * torch.empty((), dtype=self.dtype).element_size()
+                n += sp.kv_heads * (sp.head_dim + sp.value_dim) * torch.empty((), dtype=self.dtype).element_size()
         return n

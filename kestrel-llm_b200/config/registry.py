@@ -43,6 +43,8 @@ def resolve_architecture(name: str) -> Architecture:
 
 
 def architecture_of(raw: Dict[str, Any]) -> str:
+    if isinstance(raw.get("architecture"), str) and "architectures" not in raw:
+        return raw["architecture"]           # configurations that name their one model class directly
     archs = raw.get("architectures")
     if not archs or not isinstance(archs, list) or not isinstance(archs[0], str):
         raise ConfigError("config.json: 'architectures' must name the model class, e.g. "

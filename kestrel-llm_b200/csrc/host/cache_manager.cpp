@@ -13,7 +13,8 @@
 //  * pages for a step's tokens are reserved before the step runs; a reservation either gets
 //    all pages it needs in every group or changes nothing;
 //  * commit() advances the request's length and, in windowed groups, gives back pages that
-//    no later query can reach (all their positions < length - window + 1);
+//    no later query can reach (all their positions < length - window + 1) - except the pages of
+//    the request's first `keep_first` tokens, where the group's layers keep those visible;
 //  * release() gives back everything the request holds, in every group, and its slot;
 //  * free pages are a stack: the page given back last is handed out first.
 // The manager only does bookkeeping on the host; device memory is owned by the caller.
@@ -31,6 +32,7 @@ namespace {
 
 struct Group {
     int window = 0;            // 0 = keep all keys
+    int keep_first = 0;        // a windowed group never gives back the pages of positions < keep_first
     int num_pages = 0;
     std::vector<int> free_stack;   // top = back
     std::vector<uint8_t> owned;    // 1 if handed out
@@ -65,13 +67,19 @@ int first_needed_block(const Group &g, int pos, int page_size) {
     return lo <= 0 ? 0 : lo / page_size;
 }
 
+// blocks [0, kept_blocks) of a request hold its kept first tokens
+int kept_blocks(const Group &g, int page_size) {
+    return g.window > 0 && g.keep_first > 0 ? blocks_for(g.keep_first, page_size) : 0;
+}
+
 // pages a reservation of [req.reserved_to, upto) would take in group gi
 int pages_needed(const Cache &c, const Request &r, int gi, int upto) {
     const Group &g = c.groups[gi];
     int last_block = blocks_for(upto, c.page_size);        // blocks [0, last_block)
     int have = (int)r.table[gi].size();                     // blocks ever allocated (some given back)
     int first = std::max(have, first_needed_block(g, r.length, c.page_size));
-    return std::max(0, last_block - first);
+    int kept = std::min(std::min(kept_blocks(g, c.page_size), first), last_block);
+    return std::max(0, last_block - first) + std::max(0, kept - have);
 }
 
 void give_back(Cache &c, int gi, int page) {
@@ -104,6 +112,15 @@ KESTREL_API void *kcache_create(int n_groups, const int *windows, const int *num
 }
 
 KESTREL_API void kcache_destroy(void *h) { delete (Cache *)h; }
+
+// A windowed group whose layers keep a request's first `keep_first` tokens visible holds on to
+// their pages.  Set before any request is admitted.
+KESTREL_API int kcache_set_keep_first(void *h, int group, int keep_first) {
+    Cache &c = *(Cache *)h;
+    if (group < 0 || group >= (int)c.groups.size() || keep_first < 0) return -6;
+    c.groups[group].keep_first = keep_first;
+    return 0;
+}
 
 // slot of the new request, -1 if no slot is free, -2 if the id is live already
 KESTREL_API int kcache_admit(void *h, long long id) {
@@ -168,7 +185,7 @@ KESTREL_API int kcache_reserve(void *h, long long id, int n_new) {
         int first = first_needed_block(g, r.length, c.page_size);
         while ((int)t.size() < last_block) {
             int b = (int)t.size();
-            if (b < first) {            // behind the window already: never allocated
+            if (b < first && b >= kept_blocks(g, c.page_size)) {            // behind the window already: never allocated
                 t.push_back(-1);
                 r.first_live[gi] = std::max(r.first_live[gi], b + 1);
                 continue;
@@ -196,7 +213,7 @@ KESTREL_API int kcache_commit(void *h, long long id, int n_new) {
         Group &g = c.groups[gi];
         if (g.window <= 0) continue;
         int first = std::min(first_needed_block(g, r.length, c.page_size), (int)r.table[gi].size());
-        for (int b = r.first_live[gi]; b < first; ++b) {
+        for (int b = std::max(r.first_live[gi], kept_blocks(g, c.page_size)); b < first; ++b) {
             if (r.table[gi][b] >= 0) {
                 give_back(c, (int)gi, r.table[gi][b]);
                 r.table[gi][b] = -1;

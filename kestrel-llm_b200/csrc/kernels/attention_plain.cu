@@ -11,6 +11,12 @@
 // (lo, p) alone: a token's result is bit-identical however the step was cut or batched.
 // Works for any head size up to 256 and any numbers of heads.  It is the attention of the
 // true 32-bit path and the twin that the fast kernels are tested against.
+//
+// Three options beyond the reference's attention, each off by default: `keep_first` tokens at
+// the start of a request stay visible to a windowed layer after they have left the window (the
+// keys are then positions 0..min(keep_first, lo)-1 followed by lo..p, walked in this order);
+// values may have a size `vd` of their own (the V planes are [page][kv_head][slot][vd]); and
+// `gate`, float32 [T, nq], multiplies each head's output.
 #include "common.cuh"
 #include <math.h>
 
@@ -23,7 +29,8 @@ __global__ void __launch_bounds__(PA_WARPS * 32)
 attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, const T *__restrict__ v_cache,
                        const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                        const int *__restrict__ block_table, int table_stride, int page_size,
-                       T *__restrict__ out, int nq, int nkv, int hd, int window, float scale) {
+                       T *__restrict__ out, int nq, int nkv, int hd, int vd, int window, int keep_first,
+                       const float *__restrict__ gate, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     int t = blockIdx.x, h = blockIdx.y;
@@ -32,7 +39,9 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
     int pos = positions[t];
     int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int *table = block_table + (size_t)seq_of_token[t] * table_stride;
-    int per_lane = (hd + 31) / 32;
+    int per_lane = (hd + 31) / 32, per_lane_v = (vd + 31) / 32;
+    int n_kept = window > 0 ? min(keep_first, lo) : 0;      // visible keys before the window
+    int n_keys = n_kept + (pos - lo + 1);
 
     float qv[PA_MAX_PER_LANE], acc[PA_MAX_PER_LANE];
     const T *qrow = q + ((size_t)t * nq + h) * hd;
@@ -44,19 +53,20 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
     }
     float m = -INFINITY, l = 0.f;
 
-    for (int base = lo + warp * PA_KEYS; base <= pos; base += PA_WARPS * PA_KEYS) {
+    for (int base = warp * PA_KEYS; base < n_keys; base += PA_WARPS * PA_KEYS) {
         float sc[PA_KEYS];
         const T *vrow[PA_KEYS];
 #pragma unroll
         for (int u = 0; u < PA_KEYS; ++u) {
-            int s = base + u;
+            int j = base + u;
+            int s = j < n_kept ? j : lo + (j - n_kept);
             float dot = 0.f;
             vrow[u] = nullptr;
-            if (s <= pos) {
+            if (j < n_keys) {
                 int page = table[s / page_size];
-                size_t off = (((size_t)page * nkv + kvh) * page_size + (s % page_size)) * hd;
-                const T *krow = k_cache + off;
-                vrow[u] = v_cache + off;
+                size_t row = ((size_t)page * nkv + kvh) * page_size + (s % page_size);
+                const T *krow = k_cache + row * hd;
+                vrow[u] = v_cache + row * vd;
 #pragma unroll
                 for (int c = 0; c < PA_MAX_PER_LANE; ++c) {
                     int i = lane + 32 * c;
@@ -64,7 +74,7 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
                 }
             }
             dot = warp_sum(dot);
-            sc[u] = (s <= pos) ? dot * scale : -INFINITY;
+            sc[u] = (j < n_keys) ? dot * scale : -INFINITY;
         }
         float mn = m;
 #pragma unroll
@@ -81,7 +91,7 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
 #pragma unroll
                 for (int c = 0; c < PA_MAX_PER_LANE; ++c) {
                     int i = lane + 32 * c;
-                    if (c < per_lane && i < hd) acc[c] = fmaf(p, to_f32<T>(vrow[u][i]), acc[c]);
+                    if (c < per_lane_v && i < vd) acc[c] = fmaf(p, to_f32<T>(vrow[u][i]), acc[c]);
                 }
             }
         }
@@ -112,13 +122,35 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
             for (int c = 0; c < PA_MAX_PER_LANE; ++c) o[c] += sm_acc[w][lane + 32 * c] * f;
         }
         float inv = 1.0f / L;
-        T *orow = out + ((size_t)t * nq + h) * hd;
+        if (gate) inv *= gate[(size_t)t * nq + h];
+        T *orow = out + ((size_t)t * nq + h) * vd;
 #pragma unroll
         for (int c = 0; c < PA_MAX_PER_LANE; ++c) {
             int i = lane + 32 * c;
-            if (c < per_lane && i < hd) orow[i] = from_f32<T>(o[c] * inv);
+            if (c < per_lane_v && i < vd) orow[i] = from_f32<T>(o[c] * inv);
         }
     }
+}
+
+KESTREL_API int kestrel_attention_plain_ex(const void *q, const void *k_cache, const void *v_cache,
+                                           const int *positions, const int *seq_of_token,
+                                           const int *block_table, int table_stride, int page_size,
+                                           void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window,
+                                           int keep_first, const float *gate, float scale, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0 && vd > 0 && keep_first >= 0, "attention_plain: bad sizes");
+    KESTREL_REQUIRE(hd <= 32 * PA_MAX_PER_LANE && vd <= 32 * PA_MAX_PER_LANE, "attention_plain: head size %d / %d exceeds %d", hd, vd, 32 * PA_MAX_PER_LANE);
+    KESTREL_REQUIRE(nq <= 65535, "attention_plain: %d query heads exceed the grid", nq);
+    dim3 grid(T, nq);
+    if (dtype == KESTREL_F32)
+        kestrel_launch(attention_plain_kernel<float>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const float *)q, (const float *)k_cache, (const float *)v_cache, positions, seq_of_token,
+            block_table, table_stride, page_size, (float *)out, nq, nkv, hd, vd, window, keep_first, gate, scale);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, positions,
+            seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)out, nq, nkv, hd, vd, window, keep_first, gate, scale);
+    else
+        return kestrel_fail(-2, "attention_plain: unknown dtype %d", dtype);
+    return kestrel_check_launch("attention_plain");
 }
 
 KESTREL_API int kestrel_attention_plain(const void *q, const void *k_cache, const void *v_cache,
@@ -126,18 +158,6 @@ KESTREL_API int kestrel_attention_plain(const void *q, const void *k_cache, cons
                                         const int *block_table, int table_stride, int page_size,
                                         void *out, int dtype, int T, int nq, int nkv, int hd, int window,
                                         float scale, cudaStream_t stream) {
-    if (T == 0) return 0;
-    KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0, "attention_plain: bad sizes");
-    KESTREL_REQUIRE(hd <= 32 * PA_MAX_PER_LANE, "attention_plain: head size %d exceeds %d", hd, 32 * PA_MAX_PER_LANE);
-    KESTREL_REQUIRE(nq <= 65535, "attention_plain: %d query heads exceed the grid", nq);
-    dim3 grid(T, nq);
-    if (dtype == KESTREL_F32)
-        kestrel_launch(attention_plain_kernel<float>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const float *)q, (const float *)k_cache, (const float *)v_cache, positions, seq_of_token,
-            block_table, table_stride, page_size, (float *)out, nq, nkv, hd, window, scale);
-    else if (dtype == KESTREL_BF16)
-        kestrel_launch(attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, positions,
-            seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)out, nq, nkv, hd, window, scale);
-    else
-        return kestrel_fail(-2, "attention_plain: unknown dtype %d", dtype);
-    return kestrel_check_launch("attention_plain");
+    return kestrel_attention_plain_ex(q, k_cache, v_cache, positions, seq_of_token, block_table, table_stride, page_size, out, dtype, T,
+                                      nq, nkv, hd, hd, window, 0, nullptr, scale, stream);
 }

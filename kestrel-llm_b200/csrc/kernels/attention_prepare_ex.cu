@@ -1,0 +1,101 @@
+// The step between a fused query/key/value product and attention, for mixers whose heads are
+// not rotated and whose values may have a size of their own.
+//
+// The product's columns are [ q: nq*hd | k: nkv*hd | v: nkv*vd | gate: nq ]; the k and v parts are
+// absent (`has_kv` = 0) in a layer that attends over another layer's cache, the gate part where
+// `gate_out` is null.  Per token:
+//   q, k  <- x / sqrt(mean(x^2) + eps) per head, times a weight [hd] where one is given
+//            (`qk_norm` = 0 leaves them as they are);
+//   q -> q_out in the storage type; k, v -> the token's slot in its request's pages;
+//   gate_out[t, h] = sigmoid(gate column h), float32.
+// One warp a head row, lanes over the head's entries, sums of squares in float32 in a fixed
+// shuffle tree: a token's result does not depend on the batch.
+#include "common.cuh"
+#include <math.h>
+
+#define APX_WARPS 4
+#define APX_PER_LANE 8          // head sizes up to 256
+
+template <typename T>
+__global__ void __launch_bounds__(APX_WARPS * 32)
+attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_stride, int ld,
+                       const float *__restrict__ q_w, const float *__restrict__ k_w, int qk_norm, float eps,
+                       const int *__restrict__ positions, const int *__restrict__ seq_of_token,
+                       const int *__restrict__ block_table, int table_stride, int page_size,
+                       T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out, float *__restrict__ gate_out,
+                       int nq, int nkv, int hd, int vd, int has_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float *row = partial + (size_t)t * ld;
+    const int n_heads = nq + (has_kv ? 2 * nkv : 0);
+    size_t slot_row = 0;
+    if (has_kv) {
+        const int pos = positions[t];
+        const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
+        slot_row = (size_t)page * nkv * page_size + (pos % page_size);      // + kv head * page_size
+    }
+    for (int r = warp; r < n_heads; r += APX_WARPS) {
+        // which part: 0 = q head r, 1 = k head, 2 = v head
+        const int kind = r < nq ? 0 : (r < nq + nkv ? 1 : 2);
+        const int head = kind == 0 ? r : (kind == 1 ? r - nq : r - nq - nkv);
+        const int n = kind == 2 ? vd : hd;
+        const int col0 = kind == 0 ? head * hd : (kind == 1 ? nq * hd + head * hd : nq * hd + nkv * hd + head * vd);
+        float x[APX_PER_LANE];
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < APX_PER_LANE; ++c) {
+            const int i = lane + 32 * c;
+            float v = 0.f;
+            if (i < n)
+                for (int s = 0; s < S; ++s) v += row[(size_t)s * slice_stride + col0 + i];
+            x[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+        float mul = 1.f;
+        const float *w = nullptr;
+        if (kind != 2 && qk_norm) {
+            ss = warp_sum(ss);
+            mul = 1.0f / sqrtf(ss / (float)n + eps);
+            w = kind == 0 ? q_w : k_w;
+        }
+        T *dst = kind == 0 ? q_out + ((size_t)t * nq + head) * hd
+                           : (kind == 1 ? k_cache + (slot_row + (size_t)head * page_size) * hd
+                                        : v_cache + (slot_row + (size_t)head * page_size) * vd);
+#pragma unroll
+        for (int c = 0; c < APX_PER_LANE; ++c) {
+            const int i = lane + 32 * c;
+            if (i < n) dst[i] = from_f32<T>(w ? x[c] * mul * w[i] : x[c] * mul);
+        }
+    }
+    if (gate_out) {
+        const int col0 = nq * hd + (has_kv ? nkv * (hd + vd) : 0);
+        for (int h = threadIdx.x; h < nq; h += APX_WARPS * 32) {
+            float z = 0.f;
+            for (int s = 0; s < S; ++s) z += row[(size_t)s * slice_stride + col0 + h];
+            gate_out[(size_t)t * nq + h] = 1.0f / (1.0f + expf(-z));
+        }
+    }
+}
+
+KESTREL_API int kestrel_attn_prepare_ex(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w,
+                                        const float *k_norm_w, int qk_norm, float norm_eps, const int *positions,
+                                        const int *seq_of_token, const int *block_table, int table_stride, int page_size,
+                                        void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq,
+                                        int nkv, int hd, int vd, int has_kv, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0 && vd > 0 && S > 0, "attn_prepare_ex: bad sizes");
+    KESTREL_REQUIRE(hd <= 32 * APX_PER_LANE && vd <= 32 * APX_PER_LANE, "attn_prepare_ex: head size %d / %d exceeds %d", hd, vd, 32 * APX_PER_LANE);
+    const int need = nq * hd + (has_kv ? nkv * (hd + vd) : 0) + (gate_out ? nq : 0);
+    KESTREL_REQUIRE(ld >= need, "attn_prepare_ex: the product has %d columns, the heads need %d", ld, need);
+    if (dtype == KESTREL_F32)
+        kestrel_launch(attn_prepare_ex_kernel<float>, dim3(T), dim3(APX_WARPS * 32), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
+                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(attn_prepare_ex_kernel<__nv_bfloat16>, dim3(T), dim3(APX_WARPS * 32), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
+                       positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, gate_out, nq, nkv,
+                       hd, vd, has_kv);
+    else
+        return kestrel_fail(-2, "attn_prepare_ex: unknown dtype %d", dtype);
+    return kestrel_check_launch("attn_prepare_ex");
+}

@@ -1,0 +1,289 @@
+// Routed feed-forward: a router picks `top` of E experts per token, the tokens are grouped by
+// expert on the device (no value of the step is read on the host), two grouped products run the
+// chosen experts, and the results are summed per token in the order of the router's choice.
+//
+//   route      z = sum of the router product's slices + bias (float32); the `top` largest
+//              (lowest index first among equals), weights = softmax over the chosen logits
+//   group      pairs (token, choice) sorted by expert: offsets per expert, row <-> pair maps and
+//              a list of row tiles that never span two experts
+//   gate_up    per tile: g = Wg[e] x, u = Wu[e] x for the rows' tokens (gathered), then the
+//              expert's activation  y = min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)
+//   down       per tile: W_down[e] y, times the pair's routing weight, float32
+//   combine    out[t] = sum over the token's choices, in the order of choice
+//
+// The plain products accumulate by FMA in ascending k per output element, so a pair's result
+// depends neither on the tile it falls into nor on the other rows: the feed-forward of a token
+// is the same bits however the step is batched or cut.
+#include "common.cuh"
+#include <math.h>
+
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32)
+moe_route_kernel(const float *__restrict__ z_part, int S, size_t slice_stride, const float *__restrict__ bias, int E, int top,
+                 int *__restrict__ ids, float *__restrict__ weights) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float z[];
+    const int t = blockIdx.x, lane = threadIdx.x;
+    for (int e = lane; e < E; e += 32) {
+        float v = 0.f;
+        for (int s = 0; s < S; ++s) v += z_part[(size_t)s * slice_stride + (size_t)t * E + e];
+        z[e] = v + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    float zmax = 0.f, denom = 0.f, mine = 0.f;       // lane k keeps the k-th chosen logit
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (z[e] > best) { best = z[e]; arg = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (k == 0) zmax = best;
+        if (lane == 0) {
+            ids[(size_t)t * top + k] = arg;
+            z[arg] = -INFINITY;
+        }
+        if (lane == k % 32) mine = best;              // top <= 32
+        __syncwarp();
+    }
+    const float p = lane < top ? expf(mine - zmax) : 0.f;
+    denom = p;
+    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    if (lane < top) weights[(size_t)t * top + lane] = p / denom;
+}
+
+KESTREL_API int kestrel_moe_route(const float *z_part, int S, long long slice_stride, const float *bias, int *ids, float *weights, int T,
+                                  int E, int top, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && E > 0 && top > 0 && top <= E && top <= 32 && S > 0, "moe_route: bad sizes E=%d top=%d", E, top);
+    KESTREL_REQUIRE(E <= 8192, "moe_route: %d experts exceed 8192", E);
+    kestrel_launch(moe_route_kernel, dim3(T), dim3(32), (size_t)E * sizeof(float), stream, z_part, S, (size_t)slice_stride, bias, E, top, ids, weights);
+    return kestrel_check_launch("moe_route");
+}
+
+// ------------------------------------------------------------------------------------------
+// One block groups the P = T * top pairs by expert.
+//   offsets [E + 1]; row_pair [P]: pair of sorted row r; pair_row [P]: sorted row of a pair;
+//   tile_expert / tile_row0 [ceil(P / rows) + E]; n_tiles [1]
+// Rows of one expert are in ascending pair order (each expert's rows are ranked by a scan over
+// the pairs in order), so the grouping itself is the same for the same routing.
+// ------------------------------------------------------------------------------------------
+#define MG_THREADS 1024
+__global__ void __launch_bounds__(MG_THREADS)
+moe_group_kernel(const int *__restrict__ ids, int P, int E, int rows_per_tile, int *__restrict__ offsets, int *__restrict__ row_pair,
+                 int *__restrict__ pair_row, int *__restrict__ tile_expert, int *__restrict__ tile_row0, int *__restrict__ n_tiles) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int sh[];
+    int *cnt = sh, *off = sh + E;                     // cnt [E], off [E + 1]
+    for (int e = threadIdx.x; e < E; e += MG_THREADS) cnt[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += MG_THREADS) atomicAdd(&cnt[ids[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0, nt = 0;
+        for (int e = 0; e < E; ++e) {
+            off[e] = acc;
+            for (int r = 0; r < cnt[e]; r += rows_per_tile) {
+                tile_expert[nt] = e;
+                tile_row0[nt] = acc + r;
+                ++nt;
+            }
+            acc += cnt[e];
+        }
+        off[E] = acc;
+        *n_tiles = nt;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += MG_THREADS) offsets[e] = off[e];
+    // rank of a pair among its expert's pairs = how many earlier pairs chose the same expert; the
+    // block walks the pairs in chunks of its size, counting inside a chunk by comparison
+    __shared__ int chunk_ids[MG_THREADS];
+    for (int e = threadIdx.x; e < E; e += MG_THREADS) cnt[e] = 0;       // pairs of e in earlier chunks
+    __syncthreads();
+    for (int base = 0; base < P; base += MG_THREADS) {
+        const int p = base + threadIdx.x;
+        const int my = p < P ? ids[p] : -1;
+        chunk_ids[threadIdx.x] = my;
+        __syncthreads();
+        if (my >= 0) {
+            int before = 0;
+            for (int i = 0; i < (int)threadIdx.x; ++i) before += chunk_ids[i] == my;
+            const int r = off[my] + cnt[my] + before;
+            row_pair[r] = p;
+            pair_row[p] = r;
+        }
+        __syncthreads();
+        if (my >= 0) atomicAdd(&cnt[my], 1);
+        __syncthreads();
+    }
+}
+
+KESTREL_API int kestrel_moe_group(const int *ids, int P, int E, int rows_per_tile, int *offsets, int *row_pair, int *pair_row, int *tile_expert,
+                                  int *tile_row0, int *n_tiles, cudaStream_t stream) {
+    if (P == 0) return 0;
+    KESTREL_REQUIRE(P > 0 && E > 0 && E <= 8192 && rows_per_tile > 0, "moe_group: bad sizes");
+    kestrel_launch(moe_group_kernel, dim3(1), dim3(MG_THREADS), (size_t)(2 * E + 1) * sizeof(int), stream, ids, P, E, rows_per_tile, offsets, row_pair,
+                   pair_row, tile_expert, tile_row0, n_tiles);
+    return kestrel_check_launch("moe_group");
+}
+
+KESTREL_API int kestrel_moe_max_tiles(int P, int E, int rows_per_tile) { return (P + rows_per_tile - 1) / rows_per_tile + E; }
+
+// ------------------------------------------------------------------------------------------
+// Grouped products on the CUDA cores: tile of 64 rows x 64 features, 256 threads, 4 x 4 outputs a
+// thread, K in steps of 16 through shared memory (the plain product's scheme with an expert per
+// row tile).  GATE_UP: two accumulators (rows n and ff + n of the expert's stacked gate/up
+// matrix) and the activation as epilogue; else one accumulator times the pair's weight.
+// ------------------------------------------------------------------------------------------
+#define MP_BM 64
+#define MP_BN 64
+#define MP_BK 16
+
+__device__ __forceinline__ float expert_act(float g, float u, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+}
+
+template <typename T, bool GATE_UP>
+__global__ void __launch_bounds__(256)
+moe_gemm_plain_kernel(const T *__restrict__ x, long long ldx, const T *__restrict__ w, long long expert_stride, long long ldw,
+                      const int *__restrict__ offsets, const int *__restrict__ row_pair, const int *__restrict__ tile_expert,
+                      const int *__restrict__ tile_row0, const int *__restrict__ n_tiles, int top, const float *__restrict__ pair_weight,
+                      float limit, void *__restrict__ out, long long ldo, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.y >= *n_tiles) return;
+    __shared__ float xs[MP_BK][MP_BM + 4];
+    __shared__ float ws[GATE_UP ? 2 : 1][MP_BK][MP_BN + 4];
+    __shared__ int src_row[MP_BM];
+    const int tid = threadIdx.x;
+    const int e = tile_expert[blockIdx.y], r0 = tile_row0[blockIdx.y];
+    const int rows = min(MP_BM, offsets[e + 1] - r0);
+    const int n0 = blockIdx.x * MP_BN;
+    const T *we = w + (size_t)e * expert_stride;
+    if (tid < MP_BM) src_row[tid] = tid < rows ? (GATE_UP ? row_pair[r0 + tid] / top : r0 + tid) : -1;
+    __syncthreads();
+    const int ty = tid / 16, tx = tid % 16;
+    float acc[GATE_UP ? 2 : 1][4][4];
+#pragma unroll
+    for (int a = 0; a < (GATE_UP ? 2 : 1); ++a)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[a][i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += MP_BK) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int idx = tid + 256 * q;
+            const int r = idx / MP_BK, kk = idx % MP_BK;
+            const int gk = k0 + kk;
+            float xv = 0.f, wv = 0.f, wv2 = 0.f;
+            if (gk < K) {
+                if (src_row[r] >= 0) xv = to_f32<T>(x[(size_t)src_row[r] * ldx + gk]);
+                if (n0 + r < N) {
+                    wv = to_f32<T>(we[(size_t)(n0 + r) * ldw + gk]);
+                    if (GATE_UP) wv2 = to_f32<T>(we[(size_t)(N + n0 + r) * ldw + gk]);
+                }
+            }
+            xs[kk][r] = xv;
+            ws[0][kk][r] = wv;
+            if (GATE_UP) ws[GATE_UP ? 1 : 0][kk][r] = wv2;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MP_BK; ++kk) {
+            float a[4], b[4], b2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = xs[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                b[j] = ws[0][kk][tx * 4 + j];
+                if (GATE_UP) b2[j] = ws[GATE_UP ? 1 : 0][kk][tx * 4 + j];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[0][i][j] = fmaf(a[i], b[j], acc[0][i][j]);
+                    if (GATE_UP) acc[GATE_UP ? 1 : 0][i][j] = fmaf(a[i], b2[j], acc[GATE_UP ? 1 : 0][i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+        const float pw = GATE_UP ? 0.f : pair_weight[row_pair[r0 + r]];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            if (GATE_UP)
+                ((T *)out)[(size_t)(r0 + r) * ldo + n] = from_f32<T>(expert_act(acc[0][i][j], acc[GATE_UP ? 1 : 0][i][j], limit));
+            else
+                ((float *)out)[(size_t)(r0 + r) * ldo + n] = acc[0][i][j] * pw;
+        }
+    }
+}
+
+// x [T, K] tokens; w [E, 2 ff, K] (gate rows, then up rows); act [P, ff] in the storage type, rows sorted by expert
+KESTREL_API int kestrel_moe_gate_up(const void *x, long long ldx, const void *w, const int *offsets, const int *row_pair, const int *tile_expert,
+                                    const int *tile_row0, const int *n_tiles, int max_tiles, int top, float limit, void *act, int dtype,
+                                    int ff, int K, cudaStream_t stream) {
+    if (max_tiles == 0) return 0;
+    KESTREL_REQUIRE(max_tiles > 0 && max_tiles <= 65535 && ff > 0 && K > 0 && top > 0, "moe_gate_up: bad sizes");
+    dim3 grid((ff + MP_BN - 1) / MP_BN, max_tiles);
+    if (dtype == KESTREL_F32)
+        kestrel_launch(moe_gemm_plain_kernel<float, true>, grid, dim3(256), 0, stream, (const float *)x, ldx, (const float *)w, (long long)2 * ff * K, (long long)K, offsets,
+                       row_pair, tile_expert, tile_row0, n_tiles, top, (const float *)nullptr, limit, act, (long long)ff, ff, K);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(moe_gemm_plain_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, (const __nv_bfloat16 *)x, ldx, (const __nv_bfloat16 *)w, (long long)2 * ff * K,
+                       (long long)K, offsets, row_pair, tile_expert, tile_row0, n_tiles, top, (const float *)nullptr, limit, act, (long long)ff, ff, K);
+    else
+        return kestrel_fail(-2, "moe_gate_up: unknown dtype %d", dtype);
+    return kestrel_check_launch("moe_gate_up");
+}
+
+// act [P, ff]; w [E, N, ff]; y [P, N] float32 = (W_down[e] act) * weight of the pair
+KESTREL_API int kestrel_moe_down(const void *act, const void *w, const int *offsets, const int *row_pair, const int *tile_expert,
+                                 const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight, float *y, int dtype, int N,
+                                 int ff, cudaStream_t stream) {
+    if (max_tiles == 0) return 0;
+    KESTREL_REQUIRE(max_tiles > 0 && max_tiles <= 65535 && ff > 0 && N > 0, "moe_down: bad sizes");
+    dim3 grid((N + MP_BN - 1) / MP_BN, max_tiles);
+    if (dtype == KESTREL_F32)
+        kestrel_launch(moe_gemm_plain_kernel<float, false>, grid, dim3(256), 0, stream, (const float *)act, (long long)ff, (const float *)w, (long long)N * ff, (long long)ff,
+                       offsets, row_pair, tile_expert, tile_row0, n_tiles, 1, pair_weight, 0.f, (void *)y, (long long)N, N, ff);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(moe_gemm_plain_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, (const __nv_bfloat16 *)act, (long long)ff, (const __nv_bfloat16 *)w,
+                       (long long)N * ff, (long long)ff, offsets, row_pair, tile_expert, tile_row0, n_tiles, 1, pair_weight, 0.f, (void *)y, (long long)N, N, ff);
+    else
+        return kestrel_fail(-2, "moe_down: unknown dtype %d", dtype);
+    return kestrel_check_launch("moe_down");
+}
+
+// out[t, n] = sum_k y[pair_row[t * top + k], n], k ascending
+__global__ void moe_combine_kernel(const float *__restrict__ y, const int *__restrict__ pair_row, int top, float *__restrict__ out, int N) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+        float v = 0.f;
+        for (int k = 0; k < top; ++k) v += y[(size_t)pair_row[(size_t)t * top + k] * N + n];
+        out[(size_t)t * N + n] = v;
+    }
+}
+
+KESTREL_API int kestrel_moe_combine(const float *y, const int *pair_row, int top, float *out, int T, int N, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && N > 0 && top > 0, "moe_combine: bad sizes");
+    kestrel_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, y, pair_row, top, out, N);
+    return kestrel_check_launch("moe_combine");
+}

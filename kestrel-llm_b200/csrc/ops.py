@@ -726,6 +726,224 @@ def attention(planner: Optional[AttentionPlanner], q: torch.Tensor, k_cache: tor
     launches += lib.kestrel_attn_planner_last_launches(planner.handle) if planner is not None else 1
 
 
+# ---- kernels around the residual stream for arrangements other than the pre-norm block ---------
+
+def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor) -> None:
+    """x[t, 2i] += sin(pos[t] * freq[i]), x[t, 2i + 1] += cos(pos[t] * freq[i]), angles in float32."""
+    _need(x, "add_sinusoid.x", torch.float32, 2)
+    _need(positions, "add_sinusoid.positions", torch.int32, 1)
+    _need(freq, "add_sinusoid.freq", torch.float32, 1)
+    T, d = x.shape
+    if positions.shape[0] != T or freq.shape[0] < (d + 1) // 2:
+        raise KernelError("add_sinusoid: shapes differ")
+    _check(library().kestrel_add_sinusoid(x.data_ptr(), positions.data_ptr(), freq.data_ptr(), T, d, _stream()))
+
+
+def add_two(residual: torch.Tensor, a: Partials, b: Optional[Partials], cast: Optional[torch.Tensor]) -> None:
+    """residual += a + b (the sums of their slices, a's first); ``cast``, if given, receives the
+    new residual stream in its own dtype."""
+    _need(residual, "add_two.residual", torch.float32, 2)
+    T, d = residual.shape
+    for p in (a, b):
+        if p is not None and (p.tokens != T or p.width != d or p.bias is not None):
+            raise KernelError("add_two: a product does not fit the residual stream, or carries a bias")
+    if cast is not None:
+        _need(cast, "add_two.cast", dims=2)
+        if cast.shape != residual.shape:
+            raise KernelError("add_two: cast and residual differ in shape")
+    _check(library().kestrel_add_two(residual.data_ptr(), a.data.data_ptr(), a.slices, a.slice_stride,
+                                     _p(b.data) if b is not None else None, b.slices if b is not None else 0,
+                                     b.slice_stride if b is not None else 0, _p(cast),
+                                     _code(cast, "add_two.cast") if cast is not None else F32, T, d, _stream()))
+
+
+def gelu_table_mul(g: Partials, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = gelu_tanh(g[t, i]) * table[ids[t], col0 + i] for the out.shape[1] columns of g."""
+    _need(table, "gelu_table_mul.table", out.dtype, 2)
+    _need(out, "gelu_table_mul.out", dims=2)
+    _need(ids, "gelu_table_mul.ids", torch.int32, 1)
+    T, n = out.shape
+    if g.tokens != T or g.width < n or ids.shape[0] != T or col0 < 0 or col0 + n > table.shape[1] or g.bias is not None:
+        raise KernelError("gelu_table_mul: shapes differ")
+    _check(library().kestrel_gelu_table_mul(g.data.data_ptr(), g.slices, g.slice_stride, g.width, table.data_ptr(), table.stride(0),
+                                            int(col0), ids.data_ptr(), out.data_ptr(), _code(out, "gelu_table_mul.out"), T, n, _stream()))
+
+
+def add_normed(residual: torch.Tensor, p: Partials, weight: torch.Tensor, eps: float) -> None:
+    """residual += y / sqrt(mean(y^2) + eps) * weight with y the sum of p's slices."""
+    _need(residual, "add_normed.residual", torch.float32, 2)
+    _need(weight, "add_normed.weight", torch.float32, 1)
+    T, d = residual.shape
+    if p.tokens != T or p.width != d or weight.shape[0] != d or p.bias is not None:
+        raise KernelError("add_normed: shapes differ")
+    _check(library().kestrel_add_normed(residual.data_ptr(), p.data.data_ptr(), p.slices, p.slice_stride, weight.data_ptr(), float(eps),
+                                        T, d, _stream()))
+
+
+def partial_columns(p: Partials, col0: int, n: int, dtype: torch.dtype) -> torch.Tensor:
+    """Columns [col0, col0 + n) of a product, summed over its slices, in ``dtype``."""
+    out = torch.empty((p.tokens, n), dtype=dtype, device=p.data.device)
+    if p.bias is not None:
+        raise KernelError("partial_columns: a bias is pending")
+    _check(library().kestrel_partial_columns(p.data.data_ptr(), p.slices, p.slice_stride, p.width, int(col0), out.data_ptr(),
+                                             _code(out, "partial_columns.out"), p.tokens, int(n), _stream()))
+    return out
+
+
+# ---- attention without rotation, values of their own size, kept first tokens, an output gate -----
+
+def attn_prepare_ex(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], qk_norm: bool, norm_eps: float,
+                    positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, q_out: torch.Tensor, gate_out: Optional[torch.Tensor],
+                    nq: int, nkv: int, hd: int, vd: int, has_kv: bool) -> None:
+    """Columns [q | k | v | gate] of a fused product: q and k divided by their root mean square per
+    head (times a weight where given), q to ``q_out``, k and v into the cache pages (absent if
+    ``has_kv`` is False), sigmoid of the gate columns to ``gate_out`` float32 [T, nq]."""
+    _need(q_out, "attn_prepare_ex.q_out", dims=2)
+    _need(block_table, "attn_prepare_ex.block_table", torch.int32, 2)
+    _need(k_cache, "attn_prepare_ex.k_cache", q_out.dtype, 4)
+    _need(v_cache, "attn_prepare_ex.v_cache", q_out.dtype, 4)
+    T = q_out.shape[0]
+    if qkv.tokens != T or q_out.shape[1] != nq * hd or qkv.bias is not None:
+        raise KernelError("attn_prepare_ex: shapes differ")
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, vd):
+        raise KernelError("attn_prepare_ex: the cache planes do not fit the heads")
+    if gate_out is not None:
+        _need(gate_out, "attn_prepare_ex.gate_out", torch.float32, 2)
+    _check(library().kestrel_attn_prepare_ex(
+        qkv.data.data_ptr(), qkv.slices, qkv.slice_stride, qkv.width, _p(q_norm_w), _p(k_norm_w), 1 if qk_norm else 0, float(norm_eps),
+        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
+        k_cache.data_ptr(), v_cache.data_ptr(), q_out.data_ptr(), _p(gate_out), _code(q_out, "attn_prepare_ex.q_out"), T, nq, nkv, hd, vd,
+        1 if has_kv else 0, _stream()))
+
+
+def attention_plain_ex(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
+                       seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, out: torch.Tensor, nq: int, nkv: int,
+                       hd: int, vd: int, window: int, keep_first: int, gate: Optional[torch.Tensor], scale: float) -> None:
+    """`attention_plain` with values of size ``vd``, the first ``keep_first`` keys of a request
+    visible beyond the window, and each head's output multiplied by ``gate`` [T, nq]."""
+    _need(q, "attention.q", dims=2)
+    _need(out, "attention.out", q.dtype, 2)
+    _need(k_cache, "attention.k_cache", q.dtype, 4)
+    _need(v_cache, "attention.v_cache", q.dtype, 4)
+    _need(block_table, "attention.block_table", torch.int32, 2)
+    T = q.shape[0]
+    if q.shape[1] != nq * hd or out.shape != (T, nq * vd):
+        raise KernelError("attention: shapes differ")
+    if gate is not None:
+        _need(gate, "attention.gate", torch.float32, 2)
+    _check(library().kestrel_attention_plain_ex(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), int(page_size), out.data_ptr(), _code(q, "attention.q"), T, nq, nkv, hd, vd, int(window), int(keep_first),
+        _p(gate), float(scale), _stream()))
+
+
+# ---- gated delta rule ------------------------------------------------------------------------
+
+def delta_conv_silu(x: Partials, conv_w: torch.Tensor, state: torch.Tensor, tail_off: int, batch, out: torch.Tensor) -> None:
+    """out[t, c] = silu(causal convolution over time of x's first C columns), C = conv_w.shape[0];
+    inputs before the step come from, and the last taps - 1 inputs go to, each request's state slot
+    (``state`` float32 [slots, size], the tail [taps - 1, C] at ``tail_off``)."""
+    _need(conv_w, "delta_conv.w", torch.float32, 2)
+    _need(state, "delta_conv.state", torch.float32, 2)
+    _need(out, "delta_conv.out", torch.float32, 2)
+    C, taps = conv_w.shape
+    T = out.shape[0]
+    if x.tokens != T or x.width < C or out.shape[1] != C or x.bias is not None:
+        raise KernelError("delta_conv_silu: shapes differ")
+    _check(library().kestrel_delta_conv_silu(x.data.data_ptr(), x.slices, x.slice_stride, x.width, conv_w.data_ptr(), taps, state.data_ptr(),
+                                             state.stride(0), int(tail_off), batch.seq_of_token.data_ptr(), batch.cu_seqlens.data_ptr(),
+                                             batch.slots.data_ptr(), out.data_ptr(), T, batch.num_seqs, C, _stream()))
+    global launches
+    launches += 1 if taps > 1 else 0
+
+
+def delta_gates(act: torch.Tensor, x: Partials, col_beta: int, a: Partials, A_log: torch.Tensor, dt_bias: torch.Tensor,
+                qn: torch.Tensor, kn: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, H: int, G: int, d: int) -> None:
+    """Unit query and key vectors (queries scaled by d^-1/2), beta = sigmoid, decay = exp(-exp(A_log) softplus(a + dt_bias))."""
+    for t, n in ((act, "act"), (qn, "qn"), (kn, "kn"), (decay, "decay"), (beta, "beta")):
+        _need(t, f"delta_gates.{n}", torch.float32, 2)
+    T = act.shape[0]
+    if a.tokens != T or a.width != H * d or qn.shape != (T, G * d) or decay.shape != (T, H * d) or beta.shape != (T, H):
+        raise KernelError("delta_gates: shapes differ")
+    _check(library().kestrel_delta_gates(act.data_ptr(), act.shape[1], x.data.data_ptr(), x.slices, x.slice_stride, x.width, int(col_beta),
+                                         a.data.data_ptr(), a.slices, a.slice_stride, A_log.data_ptr(), dt_bias.data_ptr(), qn.data_ptr(),
+                                         kn.data_ptr(), decay.data_ptr(), beta.data_ptr(), T, H, G, d, _stream()))
+
+
+def delta_scan(qn: torch.Tensor, kn: torch.Tensor, decay: torch.Tensor, act: torch.Tensor, col_v: int, beta: torch.Tensor,
+               state: torch.Tensor, batch, out: torch.Tensor, H: int, G: int, d: int, dv: int) -> None:
+    """The recurrence S <- a S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over this step's
+    tokens of every request, from and to the requests' state slots."""
+    _need(out, "delta_scan.out", torch.float32, 2)
+    _need(state, "delta_scan.state", torch.float32, 2)
+    _check(library().kestrel_delta_scan(qn.data_ptr(), kn.data_ptr(), decay.data_ptr(), act.data_ptr(), act.shape[1], int(col_v), beta.data_ptr(),
+                                        state.data_ptr(), state.stride(0), batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), out.data_ptr(),
+                                        batch.num_seqs, H, G, d, dv, _stream()))
+
+
+def delta_out(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: Partials, out: torch.Tensor, H: int, dv: int) -> None:
+    """out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate) per head, in out's dtype."""
+    _need(o, "delta_out.o", torch.float32, 2)
+    _need(weight, "delta_out.weight", torch.float32, 1)
+    _need(out, "delta_out.out", dims=2)
+    T = o.shape[0]
+    if o.shape[1] != H * dv or out.shape != o.shape or gate.tokens != T or gate.width != H * dv or weight.shape[0] != dv:
+        raise KernelError("delta_out: shapes differ")
+    _check(library().kestrel_delta_out(o.data_ptr(), weight.data_ptr(), float(eps), gate.data.data_ptr(), gate.slices, gate.slice_stride,
+                                       out.data_ptr(), _code(out, "delta_out.out"), T, H, dv, _stream()))
+
+
+# ---- routed feed-forward -----------------------------------------------------------------------
+
+MOE_TILE_ROWS = 64
+
+
+def moe_route(z: Partials, bias: Optional[torch.Tensor], top: int):
+    """(expert ids int32 [T, top], weights float32 [T, top]): the ``top`` largest router logits of
+    each token and the softmax over them."""
+    T, E = z.tokens, z.width
+    ids = torch.empty((T, top), dtype=torch.int32, device=z.data.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=z.data.device)
+    _check(library().kestrel_moe_route(z.data.data_ptr(), z.slices, z.slice_stride, _p(bias), ids.data_ptr(), w.data_ptr(), T, E, top,
+                                       _stream()))
+    return ids, w
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                limit: float) -> torch.Tensor:
+    """The chosen experts' outputs, weighted and summed per token: float32 [T, width].
+    w_gate_up [E, 2 ff, width] (gate rows, then up rows), w_down [E, width, ff]."""
+    _need(x, "moe.x", dims=2)
+    _need(w_gate_up, "moe.w_gate_up", x.dtype, 3)
+    _need(w_down, "moe.w_down", x.dtype, 3)
+    T, K = x.shape
+    E, ff2, _ = w_gate_up.shape
+    ff, top = ff2 // 2, ids.shape[1]
+    N = w_down.shape[1]
+    if w_gate_up.shape[2] != K or w_down.shape != (E, N, ff) or ids.shape[0] != T:
+        raise KernelError("moe_experts: shapes differ")
+    lib, dev, P = library(), x.device, T * top
+    max_tiles = lib.kestrel_moe_max_tiles(P, E, MOE_TILE_ROWS)
+    meta = torch.empty((E + 1) + 2 * P + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
+    offsets, row_pair, pair_row = meta[:E + 1], meta[E + 1:E + 1 + P], meta[E + 1 + P:E + 1 + 2 * P]
+    o = E + 1 + 2 * P
+    tile_expert, tile_row0, n_tiles = meta[o:o + max_tiles], meta[o + max_tiles:o + 2 * max_tiles], meta[o + 2 * max_tiles:]
+    _check(lib.kestrel_moe_group(ids.data_ptr(), P, E, MOE_TILE_ROWS, offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(),
+                                 tile_expert.data_ptr(), tile_row0.data_ptr(), n_tiles.data_ptr(), _stream()))
+    act = torch.empty((P, ff), dtype=x.dtype, device=dev)
+    _check(lib.kestrel_moe_gate_up(x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(),
+                                   tile_expert.data_ptr(), tile_row0.data_ptr(), n_tiles.data_ptr(), max_tiles, top, float(limit),
+                                   act.data_ptr(), _code(x, "moe.x"), ff, K, _stream()))
+    y = torch.empty((P, N), dtype=torch.float32, device=dev)
+    _check(lib.kestrel_moe_down(act.data_ptr(), w_down.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), tile_expert.data_ptr(),
+                                tile_row0.data_ptr(), n_tiles.data_ptr(), max_tiles, weights.data_ptr(), y.data_ptr(), _code(x, "moe.x"), N, ff,
+                                _stream()))
+    out = torch.empty((T, N), dtype=torch.float32, device=dev)
+    _check(lib.kestrel_moe_combine(y.data_ptr(), pair_row.data_ptr(), top, out.data_ptr(), T, N, _stream()))
+    return out
+
+
 # ---- the step program and its runner ---------------------------------------------------------
 PHASES = {name[4:].lower(): value for name, value in _cdecl.constants().items() if name.startswith("KPH_") and name != "KPH_COUNT"}
 PHASE_COUNT = _cdecl.constants()["KPH_COUNT"]

@@ -43,6 +43,8 @@ typedef struct CUstream_st *kestrel_stream_t;
  * ========================================================================================== */
 KESTREL_API void *kcache_create(int n_groups, const int *windows, const int *num_pages, int page_size, int max_requests, int max_blocks_per_request);
 KESTREL_API void kcache_destroy(void *h);
+/* a windowed group also keeps the pages of its requests' first `keep_first` tokens (call before any request is admitted); 0 done, -6 no such group */
+KESTREL_API int kcache_set_keep_first(void *h, int group, int keep_first);
 /* slot of the new request; -1 no slot free; -2 the id is live already */
 KESTREL_API int kcache_admit(void *h, long long id);
 /* 1 if kcache_reserve(id, n_new) would succeed, 0 if pages are short, negative on misuse */
@@ -150,6 +152,38 @@ KESTREL_API int kestrel_swiglu(const float *partial, int S, long long slice_stri
 /* rot_mode: 0 pairs dimension j with j + rot/2 (rotate-half), 1 pairs 2j with 2j + 1 (interleaved); rot_scale multiplies cos and sin */
 KESTREL_API int kestrel_attn_prepare(const float *partial, int S, long long slice_stride, const float *bias, const float *q_norm_w, const float *k_norm_w, float norm_eps, const float *inv_freq, int rot, int rot_mode, float rot_scale, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, int dtype, int T, int nq, int nkv, int hd, int write_kv, kestrel_stream_t stream);
 KESTREL_API int kestrel_reduce_partials(const float *partial, int S, long long slice_stride, const float *bias, void *out, int out_dtype, int T, int width, kestrel_stream_t stream);
+
+/* ---- kernels around the residual stream for other arrangements than the pre-norm block (stream_ops.cu) ---- */
+/* x[t, 2i] += sin(pos[t] freq[i]), x[t, 2i + 1] += cos(pos[t] freq[i]) */
+KESTREL_API int kestrel_add_sinusoid(float *x, const int *positions, const float *freq, int T, int d, kestrel_stream_t stream);
+/* residual += sum of a's slices + sum of b's slices (b may be NULL); cast = residual in the storage type (may be NULL) */
+KESTREL_API int kestrel_add_two(float *residual, const float *a, int Sa, long long stride_a, const float *b, int Sb, long long stride_b, void *cast, int cast_dtype, int T, int d, kestrel_stream_t stream);
+/* out[t, i] = gelu_tanh(sum of g's slices at [t, i]) * table[ids[t], col0 + i], i < n; table and out in the storage type */
+KESTREL_API int kestrel_gelu_table_mul(const float *g, int S, long long slice_stride, int ld, const void *table, int table_ld, int col0, const int *ids, void *out, int dtype, int T, int n, kestrel_stream_t stream);
+/* y = sum of p's slices; residual[t] += y / sqrt(mean(y^2) + eps) * w */
+KESTREL_API int kestrel_add_normed(float *residual, const float *p, int S, long long slice_stride, const float *w, float eps, int T, int d, kestrel_stream_t stream);
+/* out[t, i] = sum of p's slices at [t, col0 + i], i < n, in the storage type */
+KESTREL_API int kestrel_partial_columns(const float *p, int S, long long slice_stride, int ld, int col0, void *out, int dtype, int T, int n, kestrel_stream_t stream);
+
+/* ---- attention without rotation, with values of their own size, kept first tokens and an output gate ---- */
+/* product columns [q: nq hd | k: nkv hd | v: nkv vd | gate: nq]; k, v absent if has_kv = 0, gate if gate_out is NULL; qk_norm: q, k / sqrt(mean(x^2) + eps) per head, times q_norm_w / k_norm_w [hd] where given */
+KESTREL_API int kestrel_attn_prepare_ex(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w, const float *k_norm_w, int qk_norm, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
+/* the plain attention with a value size vd, the first keep_first keys of a request visible beyond the window, and head outputs multiplied by gate [T, nq] (may be NULL) */
+KESTREL_API int kestrel_attention_plain_ex(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, kestrel_stream_t stream);
+
+/* ---- gated delta rule with a decay per key channel (delta_rule.cu); state slot = [S: H d dv | tail: (taps - 1) C] float32 ---- */
+KESTREL_API int kestrel_delta_conv_silu(const float *partial, int S, long long slice_stride, int ld, const float *w, int taps, float *state, long long state_stride, long long tail_off, const int *seq_of_token, const int *cu_seqlens, const int *slots, float *out, int T, int nseq, int C, kestrel_stream_t stream);
+KESTREL_API int kestrel_delta_gates(const float *act, int C, const float *partial, int S, long long slice_stride, int ld, int col_beta, const float *a_part, int Sa, long long a_stride, const float *A_log, const float *dt_bias, float *qn, float *kn, float *decay, float *beta, int T, int H, int G, int d, kestrel_stream_t stream);
+KESTREL_API int kestrel_delta_scan(const float *qn, const float *kn, const float *decay, const float *act, int C, int col_v, const float *beta, float *state, long long state_stride, const int *cu_seqlens, const int *slots, float *out, int nseq, int H, int G, int d, int dv, kestrel_stream_t stream);
+KESTREL_API int kestrel_delta_out(const float *o, const float *w, float eps, const float *g_part, int Sg, long long g_stride, void *out, int dtype, int T, int H, int dv, kestrel_stream_t stream);
+
+/* ---- routed feed-forward (moe.cu) ---- */
+KESTREL_API int kestrel_moe_route(const float *z_part, int S, long long slice_stride, const float *bias, int *ids, float *weights, int T, int E, int top, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_max_tiles(int P, int E, int rows_per_tile);
+KESTREL_API int kestrel_moe_group(const int *ids, int P, int E, int rows_per_tile, int *offsets, int *row_pair, int *pair_row, int *tile_expert, int *tile_row0, int *n_tiles, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_gate_up(const void *x, long long ldx, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, int top, float limit, void *act, int dtype, int ff, int K, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_down(const void *act, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight, float *y, int dtype, int N, int ff, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_combine(const float *y, const int *pair_row, int top, float *out, int T, int N, kestrel_stream_t stream);
 
 /* ---- matrix products ---- */
 KESTREL_API int kestrel_gemm_plain(const void *x, const void *w, float *out, int dtype, int T, int N, int K, long long ldx, long long ldw, long long ldo, kestrel_stream_t stream);

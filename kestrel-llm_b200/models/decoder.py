@@ -29,7 +29,7 @@ class DecoderModel(Part):
     def __init__(self, config, dtype: torch.dtype, device, embedding: TokenEmbedding,
                  position: Optional[PositionEncoding], blocks: Sequence[Block],
                  order: Sequence[LayerCall], final_norm: Norm, lm_head: LMHead,
-                 optional_tensors: Sequence[str] = ()):
+                 optional_tensors: Sequence[str] = (), shared_parts: Sequence[Part] = ()):
         self.config = config
         self.dtype = dtype
         self.device = torch.device(device)
@@ -40,6 +40,7 @@ class DecoderModel(Part):
         self.final_norm = final_norm
         self.lm_head = lm_head
         self.optional_tensors = tuple(optional_tensors)   # may be in a checkpoint, are not used
+        self.shared_parts = list(shared_parts)            # parts that several blocks use (a table all layers read): their weights are the model's
         n_cache = 1 + max([c.cache for c in self.order], default=-1)
         owners: List[Optional[int]] = [None] * n_cache
         for c in self.order:
@@ -79,6 +80,8 @@ class DecoderModel(Part):
         slots = self.embedding.weight_slots()
         if self.position is not None:
             slots += self.position.weight_slots()
+        for part in self.shared_parts:
+            slots += part.weight_slots()
         for b in self.blocks:
             slots += b.weight_slots()
         slots += self.final_norm.weight_slots() + self.lm_head.weight_slots()

@@ -34,10 +34,18 @@ class WeightSlot:
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values of every token, or of the last ``window`` tokens, in pages."""
+    """Keys and values of every token, or of the last ``window`` tokens, in pages.  A windowed
+    layer may keep a request's first ``keep_first`` tokens visible (their pages are then never
+    given back); values may have a size of their own."""
     kv_heads: int
     head_dim: int
     window: int = 0          # 0 = all keys
+    keep_first: int = 0      # with a window: the first tokens of a request stay
+    v_head_dim: int = 0      # 0 = head_dim
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)

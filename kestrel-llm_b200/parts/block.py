@@ -8,7 +8,7 @@ case nothing is pending.
 from __future__ import annotations
 
 import inspect
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -48,3 +48,31 @@ class PreNormBlock(Block):
         a = self.mixer.emit(prog, n, residual if self._mixer_adds else None, cache)
         n = self.norm2.emit(prog, residual, a, self.dtype)
         return self.ffn.emit(prog, n, residual if self._ffn_adds else None)
+
+
+class ParallelBlock(Block):
+    """One norm whose output both sublayers read: h = norm(x); x += mixer(h) + ffn(h); then an
+    optional per-layer token input, x += side(x, token).  The feed-forward may be absent."""
+
+    def __init__(self, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward], side, dtype: torch.dtype):
+        self.norm, self.mixer, self.ffn, self.side = norm, mixer, ffn, side
+        self.dtype = dtype
+
+    def parts(self):
+        return [p for p in (self.norm, self.mixer, self.ffn, self.side) if p is not None]
+
+    def weight_slots(self) -> List[WeightSlot]:
+        return [s for p in self.parts() for s in p.weight_slots()]
+
+    def forward(self, residual: torch.Tensor, pending, batch, cache):
+        from ..csrc import ops
+        h = self.norm.add_forward(residual, pending, self.dtype)
+        a = self.mixer.forward(h, batch, cache)
+        f = self.ffn.forward(h, batch) if self.ffn is not None else None
+        if self.side is None:
+            ops.add_two(residual, a, f, None)
+            return residual, None
+        x = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
+        ops.add_two(residual, a, f, x)
+        self.side.add_forward(residual, x, batch)
+        return residual, None

@@ -47,3 +47,21 @@ class RotaryInterleaved(RotaryHalf):
 
 class NoPositionEncoding(PositionEncoding):
     """A mixer that sees no positions (causality alone orders the tokens)."""
+
+
+class SinusoidalPositions(PositionEncoding):
+    """An absolute encoding added to the embedded tokens: entry 2i of position p is
+    sin(p * base^(-2i/width)), entry 2i + 1 the cosine of the same angle.  The frequencies are
+    made once on the host (in float64, rounded to float32); the angle and its sine and cosine
+    are float32 in the kernel.  Mixers get no rotation from it."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, device, base: float = 10000.0):
+        self.width, self.base = width, float(base)
+        i = np.arange((width + 1) // 2, dtype=np.float64)
+        self.freq = torch.from_numpy(np.power(self.base, -2.0 * i / width).astype(np.float32)).to(device)
+
+    def add_to_embedding(self, x: torch.Tensor, batch) -> None:
+        from ..csrc import ops
+        ops.add_sinusoid(x, batch.positions, self.freq)

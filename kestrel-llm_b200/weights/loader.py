@@ -88,9 +88,11 @@ def load_model(model_dir: str, dtype: str = "bfloat16", device="cuda:0"):
     raw = read_config_json(model_dir)
     arch = resolve_architecture(architecture_of(raw))
     config = arch.config_class.from_dict(raw)
-    model = arch.build(config, torch_dtype(dtype), device)
     folder = ModelFolder(model_dir)
     try:
+        if hasattr(config, "with_tensor_shapes"):      # sizes that only the checkpoint tells
+            config = config.with_tensor_shapes({n: tuple(folder.info(n)[1]) for n in folder.names()})
+        model = arch.build(config, torch_dtype(dtype), device)
         fill_from_folder(model, folder)
     finally:
         folder.close()
