@@ -128,7 +128,7 @@ def attention(W, p, m, h, eps, kv):
     q = unit_rms(linear(h, W[p + "q"]).reshape(T, H, d), eps)
     k, v = kv
     gate = sigmoid(linear(h, W[p + "g"]))                      # [T, H]
-    mask = visible(T, m["mask"]["size"], m["mask"]["keep_first"])
+    mask = visible(T, m["mask"]["size"], m["mask"]["keep_first"]) if m.get("mask") else visible(T, T, 0)    # no mask: every earlier token
     out = np.zeros((T, H, dv), dtype=F)
     for hh in range(H):
         g = hh // (H // G)
