@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
     python bench.py --workload mix14b | 32b
+    python bench.py --workload zidivik [--size a|b]
 
 Default run (the headline): decode tokens a second at batch 8, at batch 1 and 64, prefill of
 2,048 tokens, and the same decode through the Python entry point with host tokens in and out.
@@ -19,6 +20,13 @@ mixed with decode tokens under a budget of 512 tokens a step (two token tiles of
 the sizes of Qwen3-32B (64 query heads of 128 on a width of 5,120).  Each prints one JSON line
 with total, prompt and generated tokens a second, the time of all steps on the device, the
 wall-clock time over it, and the steps' fraction of their roofline.
+
+`--workload zidivik`: the Zidivik decoder (window attention with kept first tokens and shared keys,
+gated delta rule, routed experts) at layer sizes of a real model, random weights, beside the Qwen3
+dense decoder of equal width, heads, depth and active feed-forward size: a prompt of 2,048 tokens in
+one step and decode steps of 8 requests at a context of 2,048, device-timed through `Engine.step`,
+plus the device time of every kind of operation in one step of each (CUDA events around each call,
+which switch the overlap of neighbours off: compare shares).
 
 Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps, with
 a synchronize on both sides.  Every step streams all weights (15 GB) and the live requests'
@@ -245,6 +253,171 @@ def run_workload(args) -> int:
     return 0
 
 
+ZIDIVIK_SIZES = {
+    # width, heads, kv heads, head sizes, window, experts x ff (top 4), delta heads, ranks, side dim, vocab
+    "a": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=4, experts=32, top=4, ff=768,
+              d_heads=16, d_kv=4, rank=64, side=128, vocab=32000),
+    "b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=2048, keep=4, experts=64, top=4, ff=1024,
+              d_heads=32, d_kv=8, rank=128, side=256, vocab=64000),
+}
+
+
+def zidivik_raw(z):
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+           "mask": {"size": z["window"], "keep_first": z["keep"]}}
+    dlt = {"heads": z["d_heads"], "kv_heads": z["d_kv"], "dim": z["dim"], "vdim": z["vdim"], "conv": 4, "decay_rank": z["rank"], "gate_rank": z["rank"]}
+    mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"], "limit": 7.0}}
+    layers = [{"type": "attention", "mixer": att, "mlp": mlp}, {"type": "attention", "mixer": dict(att, kv_from=0), "mlp": mlp},
+              {"type": "channel_delta", "mixer": dlt, "mlp": mlp}, {"type": "attention", "mixer": att, "mlp": mlp}]
+    return {"architecture": "Zidivik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "token_side": {"dim": z["side"]},
+            "max_positions": 8192, "layers": layers}
+
+
+def run_zidivik(args) -> int:
+    """Prefill and decode of the Zidivik decoder at real layer sizes, beside the Qwen3 dense decoder of equal size."""
+    import numpy as np
+    import torch
+    from kestrel_llm_b200.config import EngineOptions, Qwen3Config, ZidivikConfig
+    from kestrel_llm_b200.config.registry import resolve_architecture
+    from kestrel_llm_b200.csrc import ops
+    from kestrel_llm_b200.engine import Engine, Entry
+    from kestrel_llm_b200.weights import fill_random_
+
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    z = ZIDIVIK_SIZES[args.size]
+    T, B, CTX = args.prefill_tokens, args.batch, 2048
+    W, K = max(3, args.warmup), max(1, min(args.steps, 32))
+    pk = peaks()
+    clocks = ClockSampler(0)
+    rng = np.random.default_rng(0)
+    timed_names = ["linear", "add_rmsnorm", "attn_prepare", "attn_prepare_ex", "attention", "attention_plain_ex", "attention_window", "qkv_prepare_fused",
+                   "gate_up_swiglu", "moe_route", "moe_experts", "delta_conv_silu", "delta_gates", "delta_scan", "delta_out", "partial_columns",
+                   "add_two", "gelu_table_mul", "add_normed", "embed", "add_sinusoid", "linear_add_into"]
+
+    def measure(cfg, label):
+        model = resolve_architecture(cfg.architecture).build(cfg, torch.bfloat16, dev)
+        fill_random_(model, 0)
+        for b in model.blocks:                  # decays and gates of a trained model's size, not of N(0, 0.02)
+            m = b.mixer
+            if hasattr(m, "dt_bias"):
+                m.dt_bias.normal_(-1.0, 1.0)
+                m.A_log.normal_(-0.5, 0.5)
+        opts = EngineOptions(dtype="bfloat16", page_size=args.page_size, batch_max=B + 1, max_model_len=CTX + T + 64,
+                             max_tokens=B * (CTX + 128) + T + 64, max_step_tokens=max(T, B), prefill_batch=T)
+        engine = Engine(model, opts)
+        engine.cache.shuffle_free(0)
+        for t in engine.cache.k + engine.cache.v:
+            if t is not None:
+                t.normal_(0.0, 0.5)
+
+        def timed(fn, n):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            clocks.active = True
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            clocks.active = False
+            return a.elapsed_time(b) / 1000.0
+
+        counter = {"i": 0}
+
+        def prefill():
+            counter["i"] += 1
+            toks = rng.integers(0, cfg.vocab_size, size=T).tolist()
+            engine.step([Entry(5000 + counter["i"], toks, (T - 1,))])
+            engine.release(5000 + counter["i"])
+        for _ in range(2):
+            prefill()
+        pre = timed(prefill, 3) / 3
+        rids = list(range(100, 100 + B))
+        ctx0 = CTX - (W + K)
+        for r in rids:                           # a context whose pages hold random values and whose state slots are as a prompt left them
+            engine.admit(r)
+            engine.cache.reserve(r, ctx0)
+            engine.cache.commit(r, ctx0)
+        engine.cache.clear_admitted()
+        nxt = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)).to(dev)
+
+        def decode():
+            if engine.graphs is not None:
+                logits = engine.step([Entry(r, (0,), (0,)) for r in rids], token_ids_dev=nxt)
+            else:
+                logits = engine.step([Entry(r, (int(t),), (0,)) for r, t in zip(rids, nxt.tolist())])
+            ops.argmax(logits, nxt)
+        for _ in range(W):
+            decode()
+        before = ops.launches + engine.graph_launches + engine.native_launches
+        dec = timed(decode, K) / K
+        launches = (ops.launches + engine.graph_launches + engine.native_launches - before) // K
+
+        # device time per kind of operation, one step of each
+        split = {}
+        if True:
+            saved, acc = {}, {}
+
+            def wrap(name, fn):
+                def inner(*a, **kw):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    out = fn(*a, **kw)
+                    e1.record()
+                    acc.setdefault(name, []).append((e0, e1))
+                    return out
+                return inner
+            for name in timed_names:
+                if hasattr(ops, name):
+                    saved[name] = getattr(ops, name)
+                    setattr(ops, name, wrap(name, saved[name]))
+            graphs, engine.graphs = engine.graphs, None
+            runner, engine.runner = engine.runner, None        # the parts' forward methods from Python: the same kernels
+            for what, fn in (("prefill", prefill), ("decode", decode)):
+                acc.clear()
+                fn()
+                torch.cuda.synchronize()
+                split[what] = {n: round(sum(a.elapsed_time(b) for a, b in ev) * 1000.0, 1) for n, ev in acc.items()}
+            engine.graphs, engine.runner = graphs, runner
+            for name, fn in saved.items():
+                setattr(ops, name, fn)
+        for r in rids:
+            engine.release(r)
+        del engine, model
+        torch.cuda.empty_cache()
+        return {"model": label, "prefill_tokens": T, "prefill_ms": round(1000 * pre, 3), "prefill_tok_s": round(T / pre, 1),
+                "decode_batch": B, "decode_context": CTX, "decode_ms": round(1000 * dec, 4), "decode_tok_s": round(B / dec, 1),
+                "launches_per_decode_step": int(launches), "device_us_per_operation": split}
+
+    raw = zidivik_raw(z)
+    zc = ZidivikConfig.from_dict(raw)
+    L = len(raw["layers"])
+    qc = Qwen3Config.from_dict(dict(QWEN3_8B, num_hidden_layers=L, hidden_size=z["width"], num_attention_heads=z["heads"],
+                                    num_key_value_heads=z["kv_heads"], head_dim=z["dim"], intermediate_size=z["top"] * z["ff"],
+                                    vocab_size=z["vocab"], max_position_embeddings=8192))
+    ours = measure(zc, "Zidivik")
+    dense = measure(qc, "Qwen3 dense, equal size")
+    clocks.close()
+    # what a Zidivik step has to do: the weights it touches once, and its arithmetic
+    D, ff, top, E = z["width"], z["ff"], z["top"], z["experts"]
+    att_w = D * (z["heads"] * z["dim"] + z["kv_heads"] * (z["dim"] + z["vdim"]) + z["heads"]) + z["heads"] * z["vdim"] * D
+    moe_active = 3 * ff * D * top
+    flops_prefill = 2.0 * T * (L * (att_w + moe_active + E * D)) + L * 4.0 * z["heads"] * z["dim"] * T * min(T, z["window"])
+    rec = {"metric": f"Zidivik prefill tokens/s at size {args.size}, bf16, beside Qwen3 dense of equal size", "value": ours["prefill_tok_s"],
+           "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ours["prefill_ms"], "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "ours", "workload": "zidivik",
+           "data": "synthetic: random weights, uniform random token ids, cache of the context filled with random values",
+           "config": dict(z, layers=[l["type"] + ("/shared keys" if "kv_from" in l["mixer"] else "") for l in raw["layers"]],
+                          page_size=args.page_size, peaks=pk["source"], parallelism="single GPU"),
+           "zidivik": ours, "dense": dense,
+           "ratio_to_dense": {"prefill": round(ours["prefill_tok_s"] / dense["prefill_tok_s"], 3), "decode": round(ours["decode_tok_s"] / dense["decode_tok_s"], 3)},
+           "prefill_flops_frac_of_peak": round(flops_prefill / (ours["prefill_ms"] / 1000.0) / (pk["bf16_tflops"] * 1e12), 4),
+           "gpu_launches": ours["launches_per_decode_step"] * K, "clocks": clocks.summary()}
+    print(json.dumps(rec))
+    return 0
+
+
 def main() -> int:
     global CONTEXT, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
@@ -258,8 +431,10 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps end (default 4096)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the prefill step (default 2048)")
-    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b"],
-                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler")
+    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b", "zidivik"],
+                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler; zidivik: the Zidivik decoder "
+                         "at real layer sizes beside Qwen3 dense of equal size")
+    ap.add_argument("--size", default="a", choices=sorted(ZIDIVIK_SIZES), help="layer sizes of --workload zidivik")
     ap.add_argument("--requests", type=int, default=0, help="requests of a workload (0: 32 for mix14b, 16 for 32b)")
     ap.add_argument("--generate", type=int, default=0, help="tokens to generate per request of a workload (0: 256 / 128)")
     ap.add_argument("--step-tokens", type=int, default=2048,
@@ -271,6 +446,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (no multi-GPU path exists)")
         return 2
+    if args.workload == "zidivik":
+        return run_zidivik(args)
     if args.workload != "decode8b":
         return run_workload(args)
     W, K = max(3, args.warmup), max(1, args.steps)

@@ -11,10 +11,14 @@
 //   down       per tile: W_down[e] y, times the pair's routing weight, float32
 //   combine    out[t] = sum over the token's choices, in the order of choice
 //
-// The plain products accumulate by FMA in ascending k per output element, so a pair's result
-// depends neither on the tile it falls into nor on the other rows: the feed-forward of a token
-// is the same bits however the step is batched or cut.
+// The plain products (float32, and bfloat16 sizes the tensor-core kernel refuses) accumulate by
+// FMA in ascending k per output element; the bfloat16 products run on the tensor cores
+// (mma.sync.m16n8k16, float32 accumulators), where an output element is a sum over k in the
+// hardware's fixed order.  Either way a pair's result depends neither on the tile it falls into
+// nor on the other rows: the feed-forward of a token is the same bits however the step is
+// batched or cut.
 #include "common.cuh"
+#include "mma_sync.cuh"
 #include <math.h>
 
 // ------------------------------------------------------------------------------------------
@@ -233,6 +237,162 @@ moe_gemm_plain_kernel(const T *__restrict__ x, long long ldx, const T *__restric
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Grouped products on the tensor cores, bfloat16: a CTA of four warps takes a tile of 64 rows of
+// one expert (warp w rows 16 w ..) against 128 weight rows - 128 features of W_down, or 64 gate
+// rows and the 64 up rows of the same features, so that the activation is the epilogue and the
+// gate/up product never reaches memory.  K in steps of 32 through a three-stage cp.async ring;
+// rows of 40 elements in shared memory keep ldmatrix free of bank conflicts.  Needs K and the row
+// strides in multiples of 8 elements and 16-byte aligned bases (cp.async of 16 bytes).
+// ------------------------------------------------------------------------------------------
+#define MM_BM 64
+#define MM_BN 128
+#define MM_BK 32
+#define MM_LDS 40
+#define MM_STAGES 3
+#define MM_SMEM (MM_STAGES * (MM_BM + MM_BN) * MM_LDS * 2)
+
+__device__ __forceinline__ void moe_cp_async16(uint32_t dst, const void *src, bool valid) {
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+
+template <bool GATE_UP>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, const __nv_bfloat16 *__restrict__ w, long long expert_stride,
+                    long long ldw, const int *__restrict__ offsets, const int *__restrict__ row_pair, const int *__restrict__ tile_expert,
+                    const int *__restrict__ tile_row0, const int *__restrict__ n_tiles, int top, const float *__restrict__ pair_weight,
+                    float limit, void *__restrict__ out, long long ldo, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.y >= *n_tiles) return;
+    extern __shared__ __align__(16) uint8_t moe_smem[];
+    __nv_bfloat16 *As = reinterpret_cast<__nv_bfloat16 *>(moe_smem);              // [stage][64][40]
+    __nv_bfloat16 *Bs = As + MM_STAGES * MM_BM * MM_LDS;                          // [stage][128][40]
+    __shared__ int src_row[MM_BM];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int e = tile_expert[blockIdx.y], r0 = tile_row0[blockIdx.y];
+    const int rows = min(MM_BM, offsets[e + 1] - r0);
+    const int n0 = blockIdx.x * (GATE_UP ? MM_BN / 2 : MM_BN);
+    const __nv_bfloat16 *we = w + (size_t)e * expert_stride;
+    if (tid < MM_BM) src_row[tid] = tid < rows ? (GATE_UP ? row_pair[r0 + tid] / top : r0 + tid) : -1;
+    __syncthreads();
+
+    // what this thread copies of every k-block: 2 chunks of 16 bytes of the rows' tile, 4 of the weights'
+    const int kc = tid & 3;
+    const __nv_bfloat16 *a_src[2], *b_src[4];
+    bool a_ok[2], b_ok[4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = (tid >> 2) + 32 * i;
+        a_ok[i] = src_row[r] >= 0;
+        a_src[i] = x + (size_t)(a_ok[i] ? src_row[r] : 0) * ldx + kc * 8;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = (tid >> 2) + 32 * i;
+        const int f = GATE_UP ? n0 + (r & 63) : n0 + r;                           // feature of this weight row
+        b_ok[i] = f < N;
+        const int wrow = GATE_UP ? (r < 64 ? f : N + f) : f;
+        b_src[i] = we + (size_t)(b_ok[i] ? wrow : 0) * ldw + kc * 8;
+    }
+    auto load = [&](int kt, int stage) {
+        const int k = kt * MM_BK + kc * 8;
+        const bool k_ok = k < K;                                                   // K is a multiple of 8: a chunk is whole or absent
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = (tid >> 2) + 32 * i;
+            moe_cp_async16((uint32_t)__cvta_generic_to_shared(As + ((size_t)stage * MM_BM + r) * MM_LDS + kc * 8),
+                           a_src[i] + (k_ok ? kt * MM_BK : 0), a_ok[i] && k_ok);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = (tid >> 2) + 32 * i;
+            moe_cp_async16((uint32_t)__cvta_generic_to_shared(Bs + ((size_t)stage * MM_BN + r) * MM_LDS + kc * 8),
+                           b_src[i] + (k_ok ? kt * MM_BK : 0), b_ok[i] && k_ok);
+        }
+    };
+    const int KT = (K + MM_BK - 1) / MM_BK;
+#pragma unroll
+    for (int s = 0; s < MM_STAGES - 1; ++s) {
+        if (s < KT) load(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    float acc[16][4];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+
+    const int a_row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, a_k = (lane >> 4) * 8;
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_k = ((lane >> 3) & 1) * 8;
+    for (int kt = 0; kt < KT; ++kt) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(MM_STAGES - 2) : "memory");
+        __syncthreads();                              // block kt has landed, and everyone has left the stage that is filled next
+        const int nk = kt + MM_STAGES - 1;
+        if (nk < KT) load(nk, nk % MM_STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int stage = kt % MM_STAGES;
+        const __nv_bfloat16 *Asg = As + (size_t)stage * MM_BM * MM_LDS, *Bsg = Bs + (size_t)stage * MM_BN * MM_LDS;
+#pragma unroll
+        for (int ks = 0; ks < MM_BK / 16; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4((uint32_t)__cvta_generic_to_shared(Asg + a_row * MM_LDS + ks * 16 + a_k), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int jp = 0; jp < 8; ++jp) {
+                uint32_t b00, b01, b10, b11;
+                ldmatrix_x4((uint32_t)__cvta_generic_to_shared(Bsg + (jp * 16 + b_row) * MM_LDS + ks * 16 + b_k), b00, b01, b10, b11);
+                mma_bf16(acc[2 * jp], a, b00, b01);
+                mma_bf16(acc[2 * jp + 1], a, b10, b11);
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + g + 8 * half;
+        if (r >= rows) continue;
+        if (GATE_UP) {
+            __nv_bfloat16 *o = (__nv_bfloat16 *)out + (size_t)(r0 + r) * ldo;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int f = n0 + j * 8 + 2 * tq + c;
+                    if (f < N) o[f] = __float2bfloat16_rn(expert_act(acc[j][2 * half + c], acc[j + 8][2 * half + c], limit));
+                }
+        } else {
+            const float pw = pair_weight[row_pair[r0 + r]];
+            float *o = (float *)out + (size_t)(r0 + r) * ldo;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int f = n0 + j * 8 + 2 * tq + c;
+                    if (f < N) o[f] = acc[j][2 * half + c] * pw;
+                }
+        }
+    }
+}
+
+static int g_moe_plain = 0;
+// 1: the bfloat16 grouped products take the CUDA-core kernel too (for tests of both)
+KESTREL_API void kestrel_moe_set_plain(int on) { g_moe_plain = on ? 1 : 0; }
+
+static bool moe_mma_takes(const void *x, long long ldx, const void *w, int K) {
+    return !g_moe_plain && K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+}
+
+template <bool GATE_UP>
+static cudaError_t moe_mma_attr() {
+    static bool done = false;
+    if (done) return cudaSuccess;
+    done = true;
+    return cudaFuncSetAttribute(moe_gemm_mma_kernel<GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
+}
+
 // x [T, K] tokens; w [E, 2 ff, K] (gate rows, then up rows); act [P, ff] in the storage type, rows sorted by expert
 KESTREL_API int kestrel_moe_gate_up(const void *x, long long ldx, const void *w, const int *offsets, const int *row_pair, const int *tile_expert,
                                     const int *tile_row0, const int *n_tiles, int max_tiles, int top, float limit, void *act, int dtype,
@@ -243,7 +403,12 @@ KESTREL_API int kestrel_moe_gate_up(const void *x, long long ldx, const void *w,
     if (dtype == KESTREL_F32)
         kestrel_launch(moe_gemm_plain_kernel<float, true>, grid, dim3(256), 0, stream, (const float *)x, ldx, (const float *)w, (long long)2 * ff * K, (long long)K, offsets,
                        row_pair, tile_expert, tile_row0, n_tiles, top, (const float *)nullptr, limit, act, (long long)ff, ff, K);
-    else if (dtype == KESTREL_BF16)
+    else if (dtype == KESTREL_BF16 && moe_mma_takes(x, ldx, w, K)) {
+        moe_mma_attr<true>();
+        kestrel_launch(moe_gemm_mma_kernel<true>, dim3((ff + MM_BN / 2 - 1) / (MM_BN / 2), max_tiles), dim3(128), MM_SMEM, stream, (const __nv_bfloat16 *)x, ldx,
+                       (const __nv_bfloat16 *)w, (long long)2 * ff * K, (long long)K, offsets, row_pair, tile_expert, tile_row0, n_tiles, top, (const float *)nullptr, limit, act,
+                       (long long)ff, ff, K);
+    } else if (dtype == KESTREL_BF16)
         kestrel_launch(moe_gemm_plain_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, (const __nv_bfloat16 *)x, ldx, (const __nv_bfloat16 *)w, (long long)2 * ff * K,
                        (long long)K, offsets, row_pair, tile_expert, tile_row0, n_tiles, top, (const float *)nullptr, limit, act, (long long)ff, ff, K);
     else
@@ -261,7 +426,12 @@ KESTREL_API int kestrel_moe_down(const void *act, const void *w, const int *offs
     if (dtype == KESTREL_F32)
         kestrel_launch(moe_gemm_plain_kernel<float, false>, grid, dim3(256), 0, stream, (const float *)act, (long long)ff, (const float *)w, (long long)N * ff, (long long)ff,
                        offsets, row_pair, tile_expert, tile_row0, n_tiles, 1, pair_weight, 0.f, (void *)y, (long long)N, N, ff);
-    else if (dtype == KESTREL_BF16)
+    else if (dtype == KESTREL_BF16 && moe_mma_takes(act, (long long)ff, w, ff)) {
+        moe_mma_attr<false>();
+        kestrel_launch(moe_gemm_mma_kernel<false>, dim3((N + MM_BN - 1) / MM_BN, max_tiles), dim3(128), MM_SMEM, stream, (const __nv_bfloat16 *)act, (long long)ff,
+                       (const __nv_bfloat16 *)w, (long long)N * ff, (long long)ff, offsets, row_pair, tile_expert, tile_row0, n_tiles, 1, pair_weight, 0.f, (void *)y,
+                       (long long)N, N, ff);
+    } else if (dtype == KESTREL_BF16)
         kestrel_launch(moe_gemm_plain_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, (const __nv_bfloat16 *)act, (long long)ff, (const __nv_bfloat16 *)w,
                        (long long)N * ff, (long long)ff, offsets, row_pair, tile_expert, tile_row0, n_tiles, 1, pair_weight, 0.f, (void *)y, (long long)N, N, ff);
     else

@@ -899,6 +899,12 @@ def delta_out(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: Partials,
 MOE_TILE_ROWS = 64
 
 
+def moe_set_plain(on: bool = True) -> None:
+    """Whether the bfloat16 grouped products of `moe_experts` take the CUDA-core kernel instead of
+    the tensor-core one (off by default).  For tests of both."""
+    library().kestrel_moe_set_plain(1 if on else 0)
+
+
 def moe_route(z: Partials, bias: Optional[torch.Tensor], top: int):
     """(expert ids int32 [T, top], weights float32 [T, top]): the ``top`` largest router logits of
     each token and the softmax over them."""

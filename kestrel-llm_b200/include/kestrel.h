@@ -180,6 +180,7 @@ KESTREL_API int kestrel_delta_out(const float *o, const float *w, float eps, con
 /* ---- routed feed-forward (moe.cu) ---- */
 KESTREL_API int kestrel_moe_route(const float *z_part, int S, long long slice_stride, const float *bias, int *ids, float *weights, int T, int E, int top, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_max_tiles(int P, int E, int rows_per_tile);
+KESTREL_API void kestrel_moe_set_plain(int on);   /* 1: the bfloat16 grouped products take the CUDA-core kernel instead of the tensor-core one; for tests of both */
 KESTREL_API int kestrel_moe_group(const int *ids, int P, int E, int rows_per_tile, int *offsets, int *row_pair, int *pair_row, int *tile_expert, int *tile_row0, int *n_tiles, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_gate_up(const void *x, long long ldx, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, int top, float limit, void *act, int dtype, int ff, int K, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_down(const void *act, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight, float *y, int dtype, int N, int ff, kestrel_stream_t stream);

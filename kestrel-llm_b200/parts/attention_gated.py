@@ -21,6 +21,7 @@ from .linear import Linear
 
 
 class GatedWindowAttention(Mixer):
+    graph_safe = True          # forward launches kernels over device tensors of the batch only
 
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, v_head_dim: int, dtype: torch.dtype, device,
                  prefix: str, scale: float, norm_eps: float, window: int = 0, keep_first: int = 0, own_kv: bool = True,

@@ -26,6 +26,7 @@ from .linear import Linear
 
 
 class ChannelDeltaMixer(Mixer):
+    graph_safe = True          # forward launches kernels over device tensors of the batch only
 
     def __init__(self, width: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, taps: int, decay_rank: int,
                  gate_rank: int, norm_eps: float, dtype: torch.dtype, device, prefix: str):

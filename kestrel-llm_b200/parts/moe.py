@@ -21,6 +21,7 @@ from .linear import Linear
 
 
 class RoutedExperts(FeedForward):
+    graph_safe = True          # forward launches kernels over device tensors of the batch only
 
     def __init__(self, width: int, inner: int, experts: int, top: int, limit: float, dtype: torch.dtype, device, prefix: str,
                  router_bias: bool = True, expert_name: str = "e{}."):
