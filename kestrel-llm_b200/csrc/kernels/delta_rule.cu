@@ -13,9 +13,9 @@
 //   conv_tail     writes the last taps-1 inputs back to the slot
 //   gates         q, k made unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q scaled by d^-1/2;
 //                 beta = sigmoid(.); a = exp(-exp(A_log[h]) softplus(. + dt_bias))
-//   scan          the recurrence; a warp takes 32 value columns of one (request, head): column j
-//                 of S stays in the registers of lane j, so S^T k and S^T q are sums inside a
-//                 thread, in ascending key channel - a token's result does not depend on how the
+//   scan          the recurrence; a value column of S stays in the registers of four lanes (a
+//                 quarter of the key channels each), so S^T k and S^T q are sums inside a thread
+//                 and one fixed shuffle tree - a token's result does not depend on how the
 //                 request was cut into steps or on the batch
 //   out_norm_gate o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) per head, in the storage type
 #include "common.cuh"
@@ -108,61 +108,118 @@ delta_gates_kernel(const float *__restrict__ act, int C, const float *__restrict
     }
 }
 
-#define DR_TC 4        // tokens staged in shared memory at a time
+#define DR_TC 8        // tokens staged in shared memory at a time
 
+__device__ __forceinline__ void dr_cp_async(float *dst, const float *src, bool vec4) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    if (vec4) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+// A CTA of four warps takes 32 value columns of one (request, head), a warp 8 of them; the four
+// lanes of a column hold interleaved quarters of its D (padded) key channels: lane part s owns
+// channels 16 m + 4 s + {0..3}.  Per token a thread does D / 4 decays and multiply-adds twice
+// (S^T k, then the write and S^T q) on four partial sums each, and the four lanes add their
+// parts in a fixed shuffle tree.  k, q, the decays, v and beta of DR_TC tokens are staged in
+// shared memory with cp.async, the next stage in flight while the current one is used.
 template <int D>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(128)
 delta_scan_kernel(const float *__restrict__ qn, const float *__restrict__ kn, const float *__restrict__ decay,
                   const float *__restrict__ act, int C, int col_v, const float *__restrict__ beta, float *__restrict__ state,
                   size_t state_stride, const int *__restrict__ cu_seqlens, const int *__restrict__ slots,
                   float *__restrict__ out, int H, int G, int d, int dv) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float sk[DR_TC][D], sq[DR_TC][D], sa[DR_TC][D];
-    const int lane = threadIdx.x;
-    const int j = blockIdx.x * 32 + lane, h = blockIdx.y, seq = blockIdx.z;
+    constexpr int STAGE = DR_TC * (3 * D + 32) + DR_TC;      // floats: k, q, a [TC][D]; v [TC][32]; beta [TC]
+    extern __shared__ float4 dr_smem4[];
+    float *sm = reinterpret_cast<float *>(dr_smem4);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int part = lane & 3, cj = lane >> 2;
+    const int jl = warp * 8 + cj, j = blockIdx.x * 32 + jl, h = blockIdx.y, seq = blockIdx.z;
     const int g = h / (H / G);
     const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
     const bool live = j < dv;
+    const bool vec4 = d % 4 == 0;
     float *Sg = state + (size_t)slots[seq] * state_stride + (size_t)h * d * dv;     // [d][dv]
-    float Sc[D];
+    float Sc[D / 16][4];
 #pragma unroll
-    for (int i = 0; i < D; ++i) Sc[i] = (i < d && live) ? Sg[(size_t)i * dv + j] : 0.f;
-    for (int tb = t0; tb < t1; tb += DR_TC) {
+    for (int m = 0; m < D / 16; ++m)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int i = 16 * m + 4 * part + c;
+            Sc[m][c] = (i < d && live) ? Sg[(size_t)i * dv + j] : 0.f;
+        }
+    for (int idx = tid; idx < 2 * STAGE; idx += 128) sm[idx] = 0.f;       // the padded channels stay zero
+    __syncthreads();
+
+    auto issue = [&](int tb, int stage) {
+        float *sk = sm + (size_t)stage * STAGE, *sq = sk + DR_TC * D, *sa = sq + DR_TC * D, *sv = sa + DR_TC * D, *sb = sv + DR_TC * 32;
+        const int per = vec4 ? d / 4 : d, w = vec4 ? 4 : 1;
+        for (int idx = tid; idx < DR_TC * per; idx += 128) {
+            const int c = idx / per, e = (idx % per) * w, t = tb + c;
+            if (t < t1) {
+                dr_cp_async(sk + c * D + e, kn + ((size_t)t * G + g) * d + e, vec4);
+                dr_cp_async(sq + c * D + e, qn + ((size_t)t * G + g) * d + e, vec4);
+                dr_cp_async(sa + c * D + e, decay + ((size_t)t * H + h) * d + e, vec4);
+            }
+        }
+        for (int idx = tid; idx < DR_TC * 32; idx += 128) {
+            const int c = idx / 32, jj = idx % 32, t = tb + c, col = blockIdx.x * 32 + jj;
+            if (t < t1 && col < dv) dr_cp_async(sv + c * 32 + jj, act + (size_t)t * C + col_v + (size_t)h * dv + col, false);
+        }
+        if (tid < DR_TC && tb + tid < t1) dr_cp_async(sb + tid, beta + (size_t)(tb + tid) * H + h, false);
+    };
+    if (t0 < t1) issue(t0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    int stage = 0;
+    for (int tb = t0; tb < t1; tb += DR_TC, stage ^= 1) {
+        if (tb + DR_TC < t1) issue(tb + DR_TC, stage ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const float *sk = sm + (size_t)stage * STAGE, *sq = sk + DR_TC * D, *sa = sq + DR_TC * D, *sv = sa + DR_TC * D, *sb = sv + DR_TC * 32;
         const int n = min(DR_TC, t1 - tb);
-        __syncwarp();
-        for (int idx = lane; idx < DR_TC * D; idx += 32) {
-            const int c = idx / D, i = idx % D;
-            const bool ok = c < n && i < d;
-            sk[c][i] = ok ? kn[((size_t)(tb + c) * G + g) * d + i] : 0.f;
-            sq[c][i] = ok ? qn[((size_t)(tb + c) * G + g) * d + i] : 0.f;
-            sa[c][i] = ok ? decay[((size_t)(tb + c) * H + h) * d + i] : 1.f;
-        }
-        __syncwarp();
         for (int c = 0; c < n; ++c) {
-            const int t = tb + c;
-            const float v = live ? act[(size_t)t * C + col_v + (size_t)h * dv + j] : 0.f;
-            const float b = beta[(size_t)t * H + h];
-            float acc = 0.f;
+            const float4 *k4 = reinterpret_cast<const float4 *>(sk + c * D), *q4 = reinterpret_cast<const float4 *>(sq + c * D),
+                         *a4 = reinterpret_cast<const float4 *>(sa + c * D);
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < D; ++i) {
-                Sc[i] *= sa[c][i];
-                acc = fmaf(Sc[i], sk[c][i], acc);
+            for (int m = 0; m < D / 16; ++m) {
+                const float4 kk = k4[4 * m + part], aa = a4[4 * m + part];
+                Sc[m][0] *= aa.x; s0 = fmaf(Sc[m][0], kk.x, s0);
+                Sc[m][1] *= aa.y; s1 = fmaf(Sc[m][1], kk.y, s1);
+                Sc[m][2] *= aa.z; s2 = fmaf(Sc[m][2], kk.z, s2);
+                Sc[m][3] *= aa.w; s3 = fmaf(Sc[m][3], kk.w, s3);
             }
-            const float u = b * (v - acc);
-            float o = 0.f;
+            float acc = (s0 + s1) + (s2 + s3);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            const float u = sb[c] * (sv[c * 32 + jl] - acc);
+            s0 = s1 = s2 = s3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < D; ++i) {
-                Sc[i] = fmaf(sk[c][i], u, Sc[i]);
-                o = fmaf(Sc[i], sq[c][i], o);
+            for (int m = 0; m < D / 16; ++m) {
+                const float4 kk = k4[4 * m + part], qq = q4[4 * m + part];
+                Sc[m][0] = fmaf(kk.x, u, Sc[m][0]); s0 = fmaf(Sc[m][0], qq.x, s0);
+                Sc[m][1] = fmaf(kk.y, u, Sc[m][1]); s1 = fmaf(Sc[m][1], qq.y, s1);
+                Sc[m][2] = fmaf(kk.z, u, Sc[m][2]); s2 = fmaf(Sc[m][2], qq.z, s2);
+                Sc[m][3] = fmaf(kk.w, u, Sc[m][3]); s3 = fmaf(Sc[m][3], qq.w, s3);
             }
-            if (live) out[((size_t)t * H + h) * dv + j] = o;
+            float o = (s0 + s1) + (s2 + s3);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (live && part == 0) out[((size_t)(tb + c) * H + h) * dv + j] = o;
         }
+        __syncthreads();                              // the stage may be filled again
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (live) {
 #pragma unroll
-        for (int i = 0; i < D; ++i)
-            if (i < d) Sg[(size_t)i * dv + j] = Sc[i];
+        for (int m = 0; m < D / 16; ++m)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int i = 16 * m + 4 * part + c;
+                if (i < d) Sg[(size_t)i * dv + j] = Sc[m][c];
+            }
     }
 }
 
@@ -219,12 +276,19 @@ KESTREL_API int kestrel_delta_scan(const float *qn, const float *kn, const float
     KESTREL_REQUIRE(H <= 65535 && nseq <= 65535, "delta_scan: grid too large");
     dim3 grid((dv + 31) / 32, H, nseq);
 #define DR_LAUNCH(D)                                                                                                                  \
-    kestrel_launch(delta_scan_kernel<D>, grid, dim3(32), 0, stream, qn, kn, decay, act, C, col_v, beta, state, (size_t)state_stride, \
-                   cu_seqlens, slots, out, H, G, d, dv)
-    if (d <= 32) DR_LAUNCH(32);
-    else if (d <= 64) DR_LAUNCH(64);
-    else if (d <= 128) DR_LAUNCH(128);
-    else DR_LAUNCH(256);
+    if ((size_t)2 * (DR_TC * (3 * D + 32) + DR_TC) * sizeof(float) > 48 * 1024) {                                                      \
+        static bool attr_set = false;                                                                                                 \
+        if (!attr_set && cudaFuncSetAttribute(delta_scan_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,                      \
+                                              (int)(2 * (DR_TC * (3 * D + 32) + DR_TC) * sizeof(float))) != cudaSuccess)            \
+            return kestrel_fail(-3, "delta_scan: cannot set the shared memory size");                                                 \
+        attr_set = true;                                                                                                              \
+    }                                                                                                                                 \
+    kestrel_launch(delta_scan_kernel<D>, grid, dim3(128), (size_t)2 * (DR_TC * (3 * D + 32) + DR_TC) * sizeof(float), stream, qn, kn, decay, act, C, col_v, \
+                   beta, state, (size_t)state_stride, cu_seqlens, slots, out, H, G, d, dv)
+    if (d <= 32) { DR_LAUNCH(32); }
+    else if (d <= 64) { DR_LAUNCH(64); }
+    else if (d <= 128) { DR_LAUNCH(128); }
+    else { DR_LAUNCH(256); }
 #undef DR_LAUNCH
     return kestrel_check_launch("delta_scan");
 }

@@ -73,8 +73,6 @@ KESTREL_API int kestrel_moe_route(const float *z_part, int S, long long slice_st
 // One block groups the P = T * top pairs by expert.
 //   offsets [E + 1]; row_pair [P]: pair of sorted row r; pair_row [P]: sorted row of a pair;
 //   tile_expert / tile_row0 [ceil(P / rows) + E]; n_tiles [1]
-// Rows of one expert are in ascending pair order (each expert's rows are ranked by a scan over
-// the pairs in order), so the grouping itself is the same for the same routing.
 // ------------------------------------------------------------------------------------------
 #define MG_THREADS 1024
 __global__ void __launch_bounds__(MG_THREADS)
@@ -104,26 +102,16 @@ moe_group_kernel(const int *__restrict__ ids, int P, int E, int rows_per_tile, i
     }
     __syncthreads();
     for (int e = threadIdx.x; e <= E; e += MG_THREADS) offsets[e] = off[e];
-    // rank of a pair among its expert's pairs = how many earlier pairs chose the same expert; the
-    // block walks the pairs in chunks of its size, counting inside a chunk by comparison
-    __shared__ int chunk_ids[MG_THREADS];
-    for (int e = threadIdx.x; e < E; e += MG_THREADS) cnt[e] = 0;       // pairs of e in earlier chunks
+    // a pair's row among its expert's rows: handed out by a counter per expert.  The order of the
+    // rows inside an expert is then not fixed, which no result depends on: every row of a grouped
+    // product is computed by itself.
+    for (int e = threadIdx.x; e < E; e += MG_THREADS) cnt[e] = 0;
     __syncthreads();
-    for (int base = 0; base < P; base += MG_THREADS) {
-        const int p = base + threadIdx.x;
-        const int my = p < P ? ids[p] : -1;
-        chunk_ids[threadIdx.x] = my;
-        __syncthreads();
-        if (my >= 0) {
-            int before = 0;
-            for (int i = 0; i < (int)threadIdx.x; ++i) before += chunk_ids[i] == my;
-            const int r = off[my] + cnt[my] + before;
-            row_pair[r] = p;
-            pair_row[p] = r;
-        }
-        __syncthreads();
-        if (my >= 0) atomicAdd(&cnt[my], 1);
-        __syncthreads();
+    for (int p = threadIdx.x; p < P; p += MG_THREADS) {
+        const int e = ids[p];
+        const int r = off[e] + atomicAdd(&cnt[e], 1);
+        row_pair[r] = p;
+        pair_row[p] = r;
     }
 }
 

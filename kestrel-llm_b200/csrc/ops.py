@@ -838,6 +838,34 @@ def attention_plain_ex(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         _p(gate), float(scale), _stream()))
 
 
+def attention_window_supported(hd: int, vd: int, nq: int, nkv: int) -> bool:
+    """Whether the tensor-core kernel of `attention_window` takes these sizes."""
+    return bool(library().kestrel_attention_window_supported(int(hd), int(vd), int(nq), int(nkv)))
+
+
+def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch, block_table: torch.Tensor, page_size: int,
+                     out: torch.Tensor, nq: int, nkv: int, hd: int, vd: int, window: int, keep_first: int, gate: Optional[torch.Tensor],
+                     scale: float) -> None:
+    """`attention_plain_ex` for bfloat16 on the tensor cores, over this step's requests as ``batch``
+    describes them (cumulative lengths, lengths after the step and the most tokens of one request)."""
+    _need(q, "attention_window.q", torch.bfloat16, 2)
+    _need(out, "attention_window.out", torch.bfloat16, 2)
+    _need(k_cache, "attention_window.k_cache", torch.bfloat16, 4)
+    _need(v_cache, "attention_window.v_cache", torch.bfloat16, 4)
+    _need(block_table, "attention_window.block_table", torch.int32, 2)
+    T = q.shape[0]
+    if q.shape[1] != nq * hd or out.shape != (T, nq * vd) or T != batch.num_tokens:
+        raise KernelError("attention_window: shapes differ")
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, vd):
+        raise KernelError("attention_window: the cache planes do not fit the heads")
+    if gate is not None:
+        _need(gate, "attention_window.gate", torch.float32, 2)
+    _check(library().kestrel_attention_window(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate), batch.cu_seqlens.data_ptr(), batch.kv_lens.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), int(page_size), int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, int(window),
+        int(keep_first), float(scale), _stream()))
+
+
 # ---- gated delta rule ------------------------------------------------------------------------
 
 def delta_conv_silu(x: Partials, conv_w: torch.Tensor, state: torch.Tensor, tail_off: int, batch, out: torch.Tensor) -> None:

@@ -170,6 +170,9 @@ KESTREL_API int kestrel_partial_columns(const float *p, int S, long long slice_s
 KESTREL_API int kestrel_attn_prepare_ex(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w, const float *k_norm_w, int qk_norm, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
 /* the plain attention with a value size vd, the first keep_first keys of a request visible beyond the window, and head outputs multiplied by gate [T, nq] (may be NULL) */
 KESTREL_API int kestrel_attention_plain_ex(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, kestrel_stream_t stream);
+/* the same attention for bfloat16 on the tensor cores (attention_window.cu); head sizes in multiples of 8 up to 256; max_count = the most tokens one request brings in this step */
+KESTREL_API int kestrel_attention_window_supported(int hd, int vd, int nq, int nkv);
+KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, kestrel_stream_t stream);
 
 /* ---- gated delta rule with a decay per key channel (delta_rule.cu); state slot = [S: H d dv | tail: (taps - 1) C] float32 ---- */
 KESTREL_API int kestrel_delta_conv_silu(const float *partial, int S, long long slice_stride, int ld, const float *w, int taps, float *state, long long state_stride, long long tail_off, const int *seq_of_token, const int *cu_seqlens, const int *slots, float *out, int T, int nseq, int C, kestrel_stream_t stream);

@@ -21,6 +21,7 @@ from .linear import Linear
 
 
 class GatedWindowAttention(Mixer):
+    force_plain = False        # tests: bfloat16 through the plain kernel too, the twin of the tensor-core one
     graph_safe = True          # forward launches kernels over device tensors of the batch only
 
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, v_head_dim: int, dtype: torch.dtype, device,
@@ -70,6 +71,11 @@ class GatedWindowAttention(Mixer):
         ops.attn_prepare_ex(fused, None, None, True, self.norm_eps, batch.positions, batch.seq_of_token, table, cache.page_size,
                             cache.k, cache.v, q, gate, self.heads, self.kv_heads, self.head_dim, self.v_head_dim, self.own_kv)
         a = torch.empty((T, self.heads * self.v_head_dim), dtype=self.dtype, device=x.device)
-        ops.attention_plain_ex(q, cache.k, cache.v, batch.positions, batch.seq_of_token, table, cache.page_size, a, self.heads,
-                               self.kv_heads, self.head_dim, self.v_head_dim, self.window, self.keep_first, gate, self.scale)
+        if self.dtype == torch.bfloat16 and not self.force_plain and \
+                ops.attention_window_supported(self.head_dim, self.v_head_dim, self.heads, self.kv_heads):
+            ops.attention_window(q, cache.k, cache.v, batch, table, cache.page_size, a, self.heads, self.kv_heads, self.head_dim,
+                                 self.v_head_dim, self.window, self.keep_first, gate, self.scale)
+        else:           # float32, and head sizes that are no multiple of 8
+            ops.attention_plain_ex(q, cache.k, cache.v, batch.positions, batch.seq_of_token, table, cache.page_size, a, self.heads,
+                                   self.kv_heads, self.head_dim, self.v_head_dim, self.window, self.keep_first, gate, self.scale)
         return self.out.forward(a)

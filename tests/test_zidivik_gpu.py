@@ -128,6 +128,25 @@ def test_attention_sees_exactly_its_keys(dtype, decode, where):
     _close(got, want, dtype, f"attention, {where}, {'decoded' if decode else 'prompt'}")
 
 
+@pytest.mark.parametrize("H,G,d,dv,size,keep,page,n,cuts", [
+    (8, 2, 64, 64, 100, 7, 16, 300, [300]), (8, 2, 64, 64, 100, 7, 16, 300, [129, 2, 140] + [1] * 29), (4, 4, 128, 128, 64, 0, 32, 200, [200]),
+    (4, 1, 128, 64, 70, 130, 16, 260, [250] + [1] * 10), (6, 3, 24, 40, None, 0, 8, 150, [75, 75]), (20, 1, 16, 16, 33, 3, 16, 90, [80] + [1] * 10),
+    (2, 2, 256, 256, 40, 2, 16, 100, [90] + [1] * 10)])
+def test_attention_on_tensor_cores_against_the_plain_kernel(H, G, d, dv, size, keep, page, n, cuts):
+    """bfloat16: the tensor-core kernel (row tiles for portions, key splits for single tokens) and the plain kernel, both
+    against the plain statement; more rows than a tile, windows over several key tiles, kept tokens beyond the window,
+    twenty heads on one kv head, head size 256."""
+    from kestrel_llm_b200.parts import GatedWindowAttention
+    fast, want, _ = _attention_case("bfloat16", H, G, d, dv, 0.35, size, keep, page, n, cuts, seed=d)
+    _close(fast, want, "bfloat16", "tensor-core attention")
+    GatedWindowAttention.force_plain = True
+    try:
+        slow, _, _ = _attention_case("bfloat16", H, G, d, dv, 0.35, size, keep, page, n, cuts, seed=d)
+    finally:
+        GatedWindowAttention.force_plain = False
+    assert np.abs(fast - slow).max() <= 2e-2 * np.abs(want).max()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_over_another_layers_pages(dtype):
     """A mixer without key and value projections attends over the pages another wrote, with its own mask and scale."""
