@@ -1,4 +1,4 @@
-"""kestrel-llm_b200: a single-GPU inference engine for the Qwen3 dense decoder on NVIDIA B200.
+"""kestrel-llm_b200: a single-GPU inference engine for the Qwen3 dense decoder and the Zidivik decoder on NVIDIA B200.
 
 Typed configuration and an architecture registry (`config`), safetensors weights by tensor
 name and a random-weights mode (`weights`), layers assembled from parts (`parts`, `models`),
