@@ -640,7 +640,8 @@ def raise_on_kernel_error() -> None:
     lib = library()
     bad = [(name, code) for name, code in (("gemm_tcgen05", lib.kestrel_gemm_tc_error()),
                                            ("attention_tc", lib.kestrel_attention_tc_error()),
-                                           ("attention_decode", lib.kestrel_attention_decode_error())) if code]
+                                           ("attention_decode", lib.kestrel_attention_decode_error()),
+                                           ("moe_tcgen05", lib.kestrel_moe_tc_error())) if code]
     if bad:
         raise KernelError("a bounded wait ran out in " + ", ".join(f"{n} (wait {c})" for n, c in bad) +
                           ": the step's results are invalid")
@@ -927,6 +928,17 @@ def delta_out(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: Partials,
 MOE_TILE_ROWS = 64
 
 
+MOE_TC_MIN_PAIRS = 1024     # from this many (token, choice) pairs on, the grouped products take the tcgen05 kernels
+_moe_tc = True
+
+
+def moe_set_tcgen05(on: bool = True) -> None:
+    """Whether the grouped products of many pairs take the tcgen05 kernels (the default) or the
+    mma.sync ones at every size.  For tests of both."""
+    global _moe_tc
+    _moe_tc = bool(on)
+
+
 def moe_set_plain(on: bool = True) -> None:
     """Whether the bfloat16 grouped products of `moe_experts` take the CUDA-core kernel instead of
     the tensor-core one (off by default).  For tests of both."""
@@ -958,6 +970,27 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     if w_gate_up.shape[2] != K or w_down.shape != (E, N, ff) or ids.shape[0] != T:
         raise KernelError("moe_experts: shapes differ")
     lib, dev, P = library(), x.device, T * top
+    act = torch.empty((P, ff), dtype=x.dtype, device=dev)
+    y = torch.empty((P, N), dtype=torch.float32, device=dev)
+    out = torch.empty((T, N), dtype=torch.float32, device=dev)
+    if _moe_tc and x.dtype == torch.bfloat16 and P >= MOE_TC_MIN_PAIRS and x.stride(0) % 8 == 0:
+        xs = torch.empty((P, K), dtype=x.dtype, device=dev)
+        if lib.kestrel_moe_tc_supported(xs.data_ptr(), act.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), ff, K):
+            rows = lib.kestrel_moe_tc_tile_rows()
+            max_tiles = lib.kestrel_moe_max_tiles(P, E, rows)
+            meta = torch.empty((E + 1) + 2 * P + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
+            offsets, row_pair, pair_row = meta[:E + 1], meta[E + 1:E + 1 + P], meta[E + 1 + P:E + 1 + 2 * P]
+            o = E + 1 + 2 * P
+            tile_expert, tile_row0, n_tiles = meta[o:o + max_tiles], meta[o + max_tiles:o + 2 * max_tiles], meta[o + 2 * max_tiles:]
+            _check(lib.kestrel_moe_group(ids.data_ptr(), P, E, rows, offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(),
+                                         tile_expert.data_ptr(), tile_row0.data_ptr(), n_tiles.data_ptr(), _stream()))
+            _check(lib.kestrel_moe_gather_rows(x.data_ptr(), x.stride(0), row_pair.data_ptr(), top, xs.data_ptr(), P, K, _stream()))
+            _check(lib.kestrel_moe_gate_up_tc(xs.data_ptr(), w_gate_up.data_ptr(), offsets.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(),
+                                              n_tiles.data_ptr(), max_tiles, float(limit), act.data_ptr(), P, E, ff, K, _stream()))
+            _check(lib.kestrel_moe_down_tc(act.data_ptr(), w_down.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), tile_expert.data_ptr(),
+                                           tile_row0.data_ptr(), n_tiles.data_ptr(), max_tiles, weights.data_ptr(), y.data_ptr(), P, E, N, ff, _stream()))
+            _check(lib.kestrel_moe_combine(y.data_ptr(), pair_row.data_ptr(), top, out.data_ptr(), T, N, _stream()))
+            return out
     max_tiles = lib.kestrel_moe_max_tiles(P, E, MOE_TILE_ROWS)
     meta = torch.empty((E + 1) + 2 * P + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
     offsets, row_pair, pair_row = meta[:E + 1], meta[E + 1:E + 1 + P], meta[E + 1 + P:E + 1 + 2 * P]
@@ -965,15 +998,12 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     tile_expert, tile_row0, n_tiles = meta[o:o + max_tiles], meta[o + max_tiles:o + 2 * max_tiles], meta[o + 2 * max_tiles:]
     _check(lib.kestrel_moe_group(ids.data_ptr(), P, E, MOE_TILE_ROWS, offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(),
                                  tile_expert.data_ptr(), tile_row0.data_ptr(), n_tiles.data_ptr(), _stream()))
-    act = torch.empty((P, ff), dtype=x.dtype, device=dev)
     _check(lib.kestrel_moe_gate_up(x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(),
                                    tile_expert.data_ptr(), tile_row0.data_ptr(), n_tiles.data_ptr(), max_tiles, top, float(limit),
                                    act.data_ptr(), _code(x, "moe.x"), ff, K, _stream()))
-    y = torch.empty((P, N), dtype=torch.float32, device=dev)
     _check(lib.kestrel_moe_down(act.data_ptr(), w_down.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), tile_expert.data_ptr(),
                                 tile_row0.data_ptr(), n_tiles.data_ptr(), max_tiles, weights.data_ptr(), y.data_ptr(), _code(x, "moe.x"), N, ff,
                                 _stream()))
-    out = torch.empty((T, N), dtype=torch.float32, device=dev)
     _check(lib.kestrel_moe_combine(y.data_ptr(), pair_row.data_ptr(), top, out.data_ptr(), T, N, _stream()))
     return out
 

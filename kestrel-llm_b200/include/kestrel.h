@@ -187,6 +187,13 @@ KESTREL_API void kestrel_moe_set_plain(int on);   /* 1: the bfloat16 grouped pro
 KESTREL_API int kestrel_moe_group(const int *ids, int P, int E, int rows_per_tile, int *offsets, int *row_pair, int *pair_row, int *tile_expert, int *tile_row0, int *n_tiles, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_gate_up(const void *x, long long ldx, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, int top, float limit, void *act, int dtype, int ff, int K, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_down(const void *act, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight, float *y, int dtype, int N, int ff, kestrel_stream_t stream);
+/* the grouped products of many tokens on tcgen05 (moe_tcgen05.cu): tiles of kestrel_moe_tc_tile_rows() rows; xs = the pairs' input rows gathered in sorted order */
+KESTREL_API int kestrel_moe_tc_tile_rows(void);
+KESTREL_API int kestrel_moe_tc_supported(const void *xs, const void *act, const void *w_gate_up, const void *w_down, int ff, int K);
+KESTREL_API int kestrel_moe_gather_rows(const void *x, long long ldx, const int *row_pair, int top, void *xs, int P, int K, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_gate_up_tc(const void *xs, const void *w, const int *offsets, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, float limit, void *act, int P, int E, int ff, int K, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_down_tc(const void *act, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight, float *y, int P, int E, int N, int ff, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_tc_error(void);
 KESTREL_API int kestrel_moe_combine(const float *y, const int *pair_row, int top, float *out, int T, int N, kestrel_stream_t stream);
 
 /* ---- matrix products ---- */

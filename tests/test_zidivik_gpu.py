@@ -256,8 +256,10 @@ def test_routed_experts_alone(dtype, E, top, ff, limit, n):
         assert np.array_equal(alone[0], got[n // 2])
 
 
-@pytest.mark.parametrize("E,top,ff,width,n", [(8, 2, 96, 64, 200), (5, 3, 72, 136, 77), (16, 4, 200, 256, 1000), (3, 1, 8, 8, 3)])
-def test_grouped_products_on_tensor_cores_against_cuda_cores(E, top, ff, width, n):
+@pytest.mark.parametrize("tcgen05", [True, False])
+@pytest.mark.parametrize("E,top,ff,width,n", [(8, 2, 96, 64, 200), (5, 3, 72, 136, 77), (16, 4, 200, 256, 1000), (3, 1, 8, 8, 3), (6, 2, 136, 200, 700),
+                                              (40, 8, 64, 72, 333)])
+def test_grouped_products_on_tensor_cores_against_cuda_cores(E, top, ff, width, n, tcgen05):
     """The bfloat16 expert products on the tensor cores against the same products on the CUDA cores: feature counts
     that do not fill a tile, a K that is no multiple of the k-block, experts without a token, more rows than a tile."""
     import torch
@@ -268,17 +270,24 @@ def test_grouped_products_on_tensor_cores_against_cuda_cores(E, top, ff, width, 
     part = RoutedExperts(width, ff, E, top, 1.25, torch.bfloat16, "cuda:0", "l0.mlp.")
     Z.load_part(part, Z.tensors_of(cfg, 1))
     x = torch.from_numpy(rng.standard_normal((n, width)).astype(np.float32)).to("cuda:0").to(torch.bfloat16)
-    fast = part.forward(x, None).reduce(torch.float32).cpu().numpy()
-    ops.moe_set_plain(True)
+    ops.moe_set_tcgen05(tcgen05)         # many pairs: tcgen05 tiles of 128 rows; off, and for few pairs: mma.sync tiles of 64
     try:
+        fast = part.forward(x, None).reduce(torch.float32).cpu().numpy()
+        alone = part.forward(x[n // 2:n // 2 + 1].contiguous(), None).reduce(torch.float32).cpu().numpy()
+        ops.moe_set_plain(True)
+        ops.moe_set_tcgen05(False)
         slow = part.forward(x, None).reduce(torch.float32).cpu().numpy()
     finally:
         ops.moe_set_plain(False)
+        ops.moe_set_tcgen05(True)
+    ops.raise_on_kernel_error()
     # same products, sums in another order, one rounding of the activation to bfloat16 in between
     assert np.abs(fast - slow).max() <= 1.5e-2 * np.abs(slow).max()
     assert np.abs(fast - slow).mean() <= 1e-3 * np.abs(slow).max()
-    alone = part.forward(x[n // 2:n // 2 + 1].contiguous(), None).reduce(torch.float32).cpu().numpy()
-    assert np.array_equal(alone[0], fast[n // 2])           # a token's result does not depend on its batch
+    if not tcgen05 or n * top < ops.MOE_TC_MIN_PAIRS:
+        assert np.array_equal(alone[0], fast[n // 2])       # the same kernel: a token's result does not depend on its batch
+    else:                                                   # the two tensor-core kernels differ in the order of their sums only
+        assert np.abs(alone[0] - fast[n // 2]).max() <= 2e-2 * np.abs(slow).max()
 
 
 def test_router_choice_and_weights():
