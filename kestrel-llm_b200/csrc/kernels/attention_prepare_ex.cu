@@ -8,8 +8,9 @@
 //            (`qk_norm` = 0 leaves them as they are);
 //   q -> q_out in the storage type; k, v -> the token's slot in its request's pages;
 //   gate_out[t, h] = sigmoid(gate column h), float32.
-// One warp a head row, lanes over the head's entries, sums of squares in float32 in a fixed
-// shuffle tree: a token's result does not depend on the batch.
+// One warp a head row (the blocks of a token share its head rows out), lanes over the head's
+// entries, sums of squares in float32 in a fixed shuffle tree: a token's result does not depend on
+// the batch.
 #include "common.cuh"
 #include <math.h>
 
@@ -35,7 +36,7 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
         const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
         slot_row = (size_t)page * nkv * page_size + (pos % page_size);      // + kv head * page_size
     }
-    for (int r = warp; r < n_heads; r += APX_WARPS) {
+    for (int r = blockIdx.y * APX_WARPS + warp; r < n_heads; r += gridDim.y * APX_WARPS) {
         // which part: 0 = q head r, 1 = k head, 2 = v head
         const int kind = r < nq ? 0 : (r < nq + nkv ? 1 : 2);
         const int head = kind == 0 ? r : (kind == 1 ? r - nq : r - nq - nkv);
@@ -46,9 +47,7 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
 #pragma unroll
         for (int c = 0; c < APX_PER_LANE; ++c) {
             const int i = lane + 32 * c;
-            float v = 0.f;
-            if (i < n)
-                for (int s = 0; s < S; ++s) v += row[(size_t)s * slice_stride + col0 + i];
+            const float v = i < n ? sum_slices(row, S, slice_stride, col0 + i) : 0.f;
             x[c] = v;
             ss = fmaf(v, v, ss);
         }
@@ -68,11 +67,10 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
             if (i < n) dst[i] = from_f32<T>(w ? x[c] * mul * w[i] : x[c] * mul);
         }
     }
-    if (gate_out) {
+    if (gate_out && blockIdx.y == 0) {
         const int col0 = nq * hd + (has_kv ? nkv * (hd + vd) : 0);
         for (int h = threadIdx.x; h < nq; h += APX_WARPS * 32) {
-            float z = 0.f;
-            for (int s = 0; s < S; ++s) z += row[(size_t)s * slice_stride + col0 + h];
+            const float z = sum_slices(row, S, slice_stride, col0 + h);
             gate_out[(size_t)t * nq + h] = 1.0f / (1.0f + expf(-z));
         }
     }
@@ -88,11 +86,14 @@ KESTREL_API int kestrel_attn_prepare_ex(const float *partial, int S, long long s
     KESTREL_REQUIRE(hd <= 32 * APX_PER_LANE && vd <= 32 * APX_PER_LANE, "attn_prepare_ex: head size %d / %d exceeds %d", hd, vd, 32 * APX_PER_LANE);
     const int need = nq * hd + (has_kv ? nkv * (hd + vd) : 0) + (gate_out ? nq : 0);
     KESTREL_REQUIRE(ld >= need, "attn_prepare_ex: the product has %d columns, the heads need %d", ld, need);
+    // few tokens: a block per four head rows, so that the step's few tokens still fill the device
+    const int n_heads = nq + (has_kv ? 2 * nkv : 0);
+    const int by = T >= 512 ? 1 : (n_heads + APX_WARPS - 1) / APX_WARPS;
     if (dtype == KESTREL_F32)
-        kestrel_launch(attn_prepare_ex_kernel<float>, dim3(T), dim3(APX_WARPS * 32), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
+        kestrel_launch(attn_prepare_ex_kernel<float>, dim3(T, by), dim3(APX_WARPS * 32), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv);
     else if (dtype == KESTREL_BF16)
-        kestrel_launch(attn_prepare_ex_kernel<__nv_bfloat16>, dim3(T), dim3(APX_WARPS * 32), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
+        kestrel_launch(attn_prepare_ex_kernel<__nv_bfloat16>, dim3(T, by), dim3(APX_WARPS * 32), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, gate_out, nq, nkv,
                        hd, vd, has_kv);
     else

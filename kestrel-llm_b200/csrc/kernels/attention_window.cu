@@ -10,12 +10,13 @@
 // step, token-major, so the heads that share a kv head read its keys and values once.  A CTA of
 // four warps takes one (request, kv head, row tile):
 //   KW = 1  tile of 64 rows, 16 a warp; every warp walks all key tiles (prompt portions);
-//   KW = 4  tile of 16 rows shared by the warps, warp w takes key tiles w, w + 4, ...; the four
-//           running (max, sum, out) states are merged in warp order at the end (decode tokens).
+//   KW = 4  tile of 16 rows shared by the warps; key tiles of 32 go round by round, four a round,
+//           one a warp, all four computed at once; the four running (max, sum, out) states are
+//           merged in warp order at the end (decode tokens).
 // The keys a tile can see are two ranges: the kept first tokens [0, ka) and the window
 // [kb, last position]; positions between them are never read (their pages may be gone).  Key
-// tiles of 64 go from the pages to shared memory with cp.async, double buffered, rows beyond a
-// range zero-filled; Q K^T and P V take their fragments with ldmatrix (V transposed), P goes
+// tiles go from the pages to shared memory with cp.async, the next round of tiles in flight
+// while the current one is used, rows beyond a range zero-filled; Q K^T and P V take their fragments with ldmatrix (V transposed), P goes
 // from the score accumulators to the second product's A operand in registers.  The grid covers
 // the longest request's row tiles for every request; CTAs beyond a request's rows leave at once,
 // so nothing of the step is read on the host and a launch can be recorded for replay.
@@ -27,7 +28,8 @@
 #include <math.h>
 
 #define AW_THREADS 128
-#define AW_BN 64
+#define AW_BN_ROWS 64        // keys of a tile, KW = 1
+#define AW_BN_KEYS 32        // keys of a tile, KW = 4
 
 struct AwParams {
     const __nv_bfloat16 *q;         // [T, nq * hd]
@@ -51,10 +53,12 @@ attention_window_kernel(const AwParams p) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int RW = 4 / KW, BM = 16 * RW, LDS = D + 8, CH = D / 8;
+    constexpr int AW_BN = KW == 1 ? AW_BN_ROWS : (D > 128 ? AW_BN_KEYS / 2 : AW_BN_KEYS);       // head size 256: shorter tiles, the same shared memory
+    constexpr int SLOTS = 2 * KW;                     // two rounds of KW tiles
     extern __shared__ __align__(16) uint8_t aw_smem[];
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(aw_smem);      // [BM][LDS]
-    __nv_bfloat16 *Ks = Qs + BM * LDS;                                   // [2][AW_BN][LDS]
-    __nv_bfloat16 *Vs = Ks + 2 * AW_BN * LDS;                            // [2][AW_BN][LDS]
+    __nv_bfloat16 *Ks = Qs + BM * LDS;                                   // [SLOTS][AW_BN][LDS]
+    __nv_bfloat16 *Vs = Ks + SLOTS * AW_BN * LDS;                        // [SLOTS][AW_BN][LDS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rt = warp % RW, ks = warp / RW;
     const int kvh = blockIdx.y, seq = blockIdx.z;
@@ -76,7 +80,7 @@ attention_window_kernel(const AwParams p) {
         if (ti < nA) { s0 = ti * AW_BN; lo = 0; up = ka; }
         else { s0 = anchorB + (ti - nA) * AW_BN; lo = kb; up = hi; }
     };
-    auto load_tile = [&](int ti, int stage) {
+    auto load_tile = [&](int ti, int slot) {
         int s0, lo, up;
         tile_range(ti, s0, lo, up);
         for (int idx = tid; idx < AW_BN * CH; idx += AW_THREADS) {
@@ -85,9 +89,14 @@ attention_window_kernel(const AwParams p) {
             size_t row = 0;
             if (in) row = ((size_t)table[s / p.page_size] * p.nkv + kvh) * p.page_size + (s % p.page_size);
             const bool k_ok = in && c * 8 < hd, v_ok = in && c * 8 < vd;
-            aw_cp_async16((uint32_t)__cvta_generic_to_shared(Ks + ((size_t)stage * AW_BN + r) * LDS + c * 8), p.k_cache + (k_ok ? row * hd + c * 8 : 0), k_ok);
-            aw_cp_async16((uint32_t)__cvta_generic_to_shared(Vs + ((size_t)stage * AW_BN + r) * LDS + c * 8), p.v_cache + (v_ok ? row * vd + c * 8 : 0), v_ok);
+            aw_cp_async16((uint32_t)__cvta_generic_to_shared(Ks + ((size_t)slot * AW_BN + r) * LDS + c * 8), p.k_cache + (k_ok ? row * hd + c * 8 : 0), k_ok);
+            aw_cp_async16((uint32_t)__cvta_generic_to_shared(Vs + ((size_t)slot * AW_BN + r) * LDS + c * 8), p.v_cache + (v_ok ? row * vd + c * 8 : 0), v_ok);
         }
+    };
+    auto load_round = [&](int rd) {                   // the KW tiles of round rd, into the slots of its parity
+#pragma unroll
+        for (int w = 0; w < KW; ++w)
+            if (rd * KW + w < n_tiles) load_tile(rd * KW + w, (rd & 1) * KW + w);
     };
     for (int idx = tid; idx < BM * CH; idx += AW_THREADS) {
         const int r = idx / CH, c = idx % CH;
@@ -99,7 +108,7 @@ attention_window_kernel(const AwParams p) {
         }
         aw_cp_async16((uint32_t)__cvta_generic_to_shared(Qs + r * LDS + c * 8), p.q + off, ok);
     }
-    load_tile(0, 0);
+    load_round(0);                                    // Q travels with the first group
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     // the two rows of this thread in its warp's 16-row tile: g and g + 8
@@ -121,13 +130,14 @@ attention_window_kernel(const AwParams p) {
     const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
     const int k_steps = (hd + 15) / 16, v_pairs = (vd + 15) / 16;
 
-    for (int ti = 0; ti < n_tiles; ++ti) {
-        const int stage = ti & 1;
-        if (ti + 1 < n_tiles) load_tile(ti + 1, stage ^ 1);          // the other stage was left by everyone at the end of the last round
+    const int n_rounds = (n_tiles + KW - 1) / KW;
+    for (int rd = 0; rd < n_rounds; ++rd) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                              // round rd has landed, and everyone has left the slots that are filled next
+        if (rd + 1 < n_rounds) load_round(rd + 1);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        __syncthreads();
-        if (ti % KW == ks) {
+        const int ti = rd * KW + ks, stage = (rd & 1) * KW + ks;
+        if (ti < n_tiles) {
             int s0, lo, up;
             tile_range(ti, s0, lo, up);
             const __nv_bfloat16 *Kg = Ks + (size_t)stage * AW_BN * LDS, *Vg = Vs + (size_t)stage * AW_BN * LDS;
@@ -198,9 +208,9 @@ attention_window_kernel(const AwParams p) {
                 }
             }
         }
-        __syncthreads();                              // the stage may be filled again
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                  // every warp is done with the tiles: their memory is free
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
         l_r[h2] += __shfl_xor_sync(0xffffffffu, l_r[h2], 1);
@@ -261,8 +271,8 @@ attention_window_kernel(const AwParams p) {
 
 template <int D, int KW>
 static int aw_launch(const AwParams &p, int nseq, int max_count, cudaStream_t stream) {
-    constexpr int BM = 16 * (4 / KW);
-    const size_t smem = (size_t)(BM + 4 * AW_BN) * (D + 8) * sizeof(__nv_bfloat16);
+    constexpr int BM = 16 * (4 / KW), AW_BN = KW == 1 ? AW_BN_ROWS : (D > 128 ? AW_BN_KEYS / 2 : AW_BN_KEYS);
+    const size_t smem = (size_t)(BM + 2 * 2 * KW * AW_BN) * (D + 8) * sizeof(__nv_bfloat16);
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(attention_window_kernel<D, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

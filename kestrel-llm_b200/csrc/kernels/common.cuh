@@ -76,3 +76,17 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+
+// Sum of a product's float32 slices at one element, in ascending slice order; the loads of four
+// slices are in flight at once (the adds keep their order, so the bits are those of a plain loop).
+__device__ __forceinline__ float sum_slices(const float *__restrict__ p, int S, size_t slice_stride, size_t off) {
+    float v = 0.f;
+    int s = 0;
+    for (; s + 4 <= S; s += 4) {
+        const float a = p[(size_t)s * slice_stride + off], b = p[(size_t)(s + 1) * slice_stride + off];
+        const float c = p[(size_t)(s + 2) * slice_stride + off], d = p[(size_t)(s + 3) * slice_stride + off];
+        v += a; v += b; v += c; v += d;
+    }
+    for (; s < S; ++s) v += p[(size_t)s * slice_stride + off];
+    return v;
+}

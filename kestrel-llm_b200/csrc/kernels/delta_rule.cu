@@ -25,9 +25,7 @@
 
 // sum of a product's slices at (token, column)
 __device__ __forceinline__ float slices_at(const float *p, int S, size_t slice_stride, size_t off) {
-    float v = 0.f;
-    for (int s = 0; s < S; ++s) v += p[(size_t)s * slice_stride + off];
-    return v;
+    return sum_slices(p, S, slice_stride, off);
 }
 
 __global__ void delta_conv_silu_kernel(const float *__restrict__ partial, int S, size_t slice_stride, int ld, const float *__restrict__ w,

@@ -30,9 +30,7 @@ moe_route_kernel(const float *__restrict__ z_part, int S, size_t slice_stride, c
     extern __shared__ float z[];
     const int t = blockIdx.x, lane = threadIdx.x;
     for (int e = lane; e < E; e += 32) {
-        float v = 0.f;
-        for (int s = 0; s < S; ++s) v += z_part[(size_t)s * slice_stride + (size_t)t * E + e];
-        z[e] = v + (bias ? bias[e] : 0.f);
+        z[e] = sum_slices(z_part, S, slice_stride, (size_t)t * E + e) + (bias ? bias[e] : 0.f);
     }
     __syncwarp();
     float zmax = 0.f, denom = 0.f, mine = 0.f;       // lane k keeps the k-th chosen logit

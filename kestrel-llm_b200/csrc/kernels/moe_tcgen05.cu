@@ -139,10 +139,12 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     }
                 } else {
                     float *o = (float *)out;
-                    if (n < N) {
+                    // the 16 rows' routing weights: lane j fetches row j's, the others get it by shuffle
+                    const float pw_mine = (lane < 16 && c + lane < valid) ? pair_weight[row_pair[t0 + c + lane]] : 0.f;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (c + j < valid) o[(size_t)(t0 + c + j) * ldo + n] = g[j] * pair_weight[row_pair[t0 + c + j]];
+                    for (int j = 0; j < 16; ++j) {
+                        const float pw = __shfl_sync(0xffffffffu, pw_mine, j);
+                        if (n < N && c + j < valid) o[(size_t)(t0 + c + j) * ldo + n] = g[j] * pw;
                     }
                 }
             }
@@ -156,13 +158,20 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     }
 }
 
+static int g_moe_tc_smem_kb = 104;
+// shared memory of a CTA's ring of stages in KB (104: two CTAs an SM; 200: one); for measurements
+KESTREL_API void kestrel_moe_tc_set_ring_kb(int kb) { g_moe_tc_smem_kb = kb < 64 ? 64 : (kb > 200 ? 200 : kb); }
+
 template <bool GATE_UP>
 static int moe_tc_launch(const CUtensorMap &mw, const CUtensorMap &mx, void *out, const int *offsets, const int *row_pair,
                          const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight,
                          float limit, int w_rows_per_expert, int up_off, int N, int K, long long ldo, cudaStream_t stream) {
     constexpr int STAGE_BYTES = (GATE_UP ? 2 : 1) * MT_BM * MT_BK * 2 + MT_BN * MT_BK * 2;
     const int num_kb = (K + MT_BK - 1) / MT_BK;
-    int stages = (200 * 1024) / STAGE_BYTES;
+    // two CTAs share an SM (half of its shared memory and at most half of TMEM each): the epilogue of
+    // one runs under the main loop of the other
+    int stages = (g_moe_tc_smem_kb * 1024) / STAGE_BYTES;
+    if (stages < 2) stages = 2;
     if (stages > num_kb) stages = num_kb < 2 ? 2 : num_kb;
     if (stages > 12) stages = 12;
     const size_t smem = (size_t)stages * STAGE_BYTES + 16 * stages + 16 + 1024;

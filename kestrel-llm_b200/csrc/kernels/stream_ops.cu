@@ -44,9 +44,7 @@ __global__ void add_two_kernel(float *__restrict__ residual, const float *__rest
     pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
-    float va = 0.f, vb = 0.f;
-    for (int s = 0; s < Sa; ++s) va += a[(size_t)s * stride_a + idx];
-    for (int s = 0; s < Sb; ++s) vb += b[(size_t)s * stride_b + idx];
+    const float va = sum_slices(a, Sa, stride_a, idx), vb = Sb > 0 ? sum_slices(b, Sb, stride_b, idx) : 0.f;
     float v = residual[idx] + (va + vb);
     residual[idx] = v;
     if (cast) cast[idx] = from_f32<TOut>(v);
@@ -83,8 +81,7 @@ __global__ void gelu_table_mul_kernel(const float *__restrict__ g, int S, size_t
     const int t = blockIdx.x;
     const TW *row = table + (size_t)ids[t] * table_ld + col0;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float z = 0.f;
-        for (int s = 0; s < S; ++s) z += g[(size_t)s * slice_stride + (size_t)t * ld + i];
+        const float z = sum_slices(g, S, slice_stride, (size_t)t * ld + i);
         out[(size_t)t * n + i] = from_f32<TOut>(gelu_tanh_f(z) * to_f32<TW>(row[i]));
     }
 }
@@ -118,8 +115,7 @@ add_normed_kernel(float *__restrict__ residual, const float *__restrict__ p, int
     const int t = blockIdx.x;
     float ss = 0.f;
     for (int i = threadIdx.x; i < d; i += AN_THREADS) {
-        float y = 0.f;
-        for (int s = 0; s < S; ++s) y += p[(size_t)s * slice_stride + (size_t)t * d + i];
+        const float y = sum_slices(p, S, slice_stride, (size_t)t * d + i);
         ys[i] = y;
         ss = fmaf(y, y, ss);
     }
@@ -154,9 +150,7 @@ __global__ void partial_columns_kernel(const float *__restrict__ p, int S, size_
     if (idx >= total) return;
     size_t t = idx / n;
     int i = (int)(idx % n);
-    float v = 0.f;
-    for (int s = 0; s < S; ++s) v += p[(size_t)s * slice_stride + t * ld + col0 + i];
-    out[idx] = from_f32<TOut>(v);
+    out[idx] = from_f32<TOut>(sum_slices(p, S, slice_stride, t * ld + col0 + i));
 }
 
 KESTREL_API int kestrel_partial_columns(const float *p, int S, long long slice_stride, int ld, int col0, void *out, int dtype, int T, int n,

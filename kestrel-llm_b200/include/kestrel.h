@@ -194,6 +194,7 @@ KESTREL_API int kestrel_moe_gather_rows(const void *x, long long ldx, const int 
 KESTREL_API int kestrel_moe_gate_up_tc(const void *xs, const void *w, const int *offsets, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, float limit, void *act, int P, int E, int ff, int K, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_down_tc(const void *act, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight, float *y, int P, int E, int N, int ff, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_tc_error(void);
+KESTREL_API void kestrel_moe_tc_set_ring_kb(int kb);   /* shared memory of a CTA's stages in KB: 104 (default) lets two CTAs share an SM, 200 gives one all of it; for measurements */
 KESTREL_API int kestrel_moe_combine(const float *y, const int *pair_row, int top, float *out, int T, int N, kestrel_stream_t stream);
 
 /* ---- matrix products ---- */
