@@ -314,15 +314,14 @@ def run_zidivik(args) -> int:
         def timed(fn, n):
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            clocks.active = True
             a.record()
             for _ in range(n):
                 fn()
             b.record()
             torch.cuda.synchronize()
-            clocks.active = False
             return a.elapsed_time(b) / 1000.0
 
+        clocks.active = True                     # the timed regions are milliseconds long: sample over the whole measurement
         counter = {"i": 0}
 
         def prefill():
@@ -330,9 +329,9 @@ def run_zidivik(args) -> int:
             toks = rng.integers(0, cfg.vocab_size, size=T).tolist()
             engine.step([Entry(5000 + counter["i"], toks, (T - 1,))])
             engine.release(5000 + counter["i"])
-        for _ in range(2):
+        for _ in range(3):
             prefill()
-        pre = timed(prefill, 3) / 3
+        pre = min(timed(prefill, 5) / 5 for _ in range(4))      # the host prepares 2,048 ids a step: the best of four rounds of five
         rids = list(range(100, 100 + B))
         ctx0 = CTX - (W + K)
         for r in rids:                           # a context whose pages hold random values and whose state slots are as a prompt left them
@@ -382,6 +381,7 @@ def run_zidivik(args) -> int:
             engine.graphs, engine.runner = graphs, runner
             for name, fn in saved.items():
                 setattr(ops, name, fn)
+        clocks.active = False
         for r in rids:
             engine.release(r)
         del engine, model
