@@ -13,8 +13,8 @@
 //   conv_tail     writes the last taps-1 inputs back to the slot
 //   gates         q, k made unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q scaled by d^-1/2;
 //                 beta = sigmoid(.); a = exp(-exp(A_log[h]) softplus(. + dt_bias))
-//   scan          the recurrence; a value column of S stays in the registers of four lanes (a
-//                 quarter of the key channels each), so S^T k and S^T q are sums inside a thread
+//   scan          the recurrence; a value column of S stays in the registers of eight lanes (an
+//                 eighth of the key channels each), so S^T k and S^T q are sums inside a thread
 //                 and one fixed shuffle tree - a token's result does not depend on how the
 //                 request was cut into steps or on the batch
 //   out_norm_gate o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) per head, in the storage type
@@ -107,6 +107,8 @@ delta_gates_kernel(const float *__restrict__ act, int C, const float *__restrict
 }
 
 #define DR_TC 8        // tokens staged in shared memory at a time
+#define DR_LPC 8       // lanes that share a value column's key channels
+#define DR_COLS (128 / DR_LPC)      // value columns of a CTA of four warps
 
 __device__ __forceinline__ void dr_cp_async(float *dst, const float *src, bool vec4) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -114,11 +116,12 @@ __device__ __forceinline__ void dr_cp_async(float *dst, const float *src, bool v
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-// A CTA of four warps takes 32 value columns of one (request, head), a warp 8 of them; the four
-// lanes of a column hold interleaved quarters of its D (padded) key channels: lane part s owns
-// channels 16 m + 4 s + {0..3}.  Per token a thread does D / 4 decays and multiply-adds twice
-// (S^T k, then the write and S^T q) on four partial sums each, and the four lanes add their
-// parts in a fixed shuffle tree.  k, q, the decays, v and beta of DR_TC tokens are staged in
+// A CTA of four warps takes DR_COLS value columns of one (request, head); the DR_LPC lanes of a
+// column hold interleaved parts of its D (padded) key channels: lane part s owns channels
+// 4 (DR_LPC m + s) + {0..3}.  Per token a thread does D / DR_LPC decays and multiply-adds twice
+// (S^T k, then the write and S^T q) on four partial sums each, and the lanes of a column add their
+// parts in a fixed shuffle tree.  The time of a token is the latency of this chain, so the parts
+// are short: with four lanes a column a token took 0.41 us, with eight it takes less.  k, q, the decays, v and beta of DR_TC tokens are staged in
 // shared memory with cp.async, the next stage in flight while the current one is used.
 template <int D>
 __global__ void __launch_bounds__(128)
@@ -128,23 +131,24 @@ delta_scan_kernel(const float *__restrict__ qn, const float *__restrict__ kn, co
                   float *__restrict__ out, int H, int G, int d, int dv) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int STAGE = DR_TC * (3 * D + 32) + DR_TC;      // floats: k, q, a [TC][D]; v [TC][32]; beta [TC]
+    constexpr int STAGE = DR_TC * (3 * D + 32) + DR_TC;      // floats: k, q, a [TC][D]; v [TC][32, DR_COLS used]; beta [TC]
+    constexpr int M = D / (4 * DR_LPC);                      // float4s of a thread's part
     extern __shared__ float4 dr_smem4[];
     float *sm = reinterpret_cast<float *>(dr_smem4);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int part = lane & 3, cj = lane >> 2;
-    const int jl = warp * 8 + cj, j = blockIdx.x * 32 + jl, h = blockIdx.y, seq = blockIdx.z;
+    const int part = lane % DR_LPC, cj = lane / DR_LPC;
+    const int jl = warp * (32 / DR_LPC) + cj, j = blockIdx.x * DR_COLS + jl, h = blockIdx.y, seq = blockIdx.z;
     const int g = h / (H / G);
     const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
     const bool live = j < dv;
     const bool vec4 = d % 4 == 0;
     float *Sg = state + (size_t)slots[seq] * state_stride + (size_t)h * d * dv;     // [d][dv]
-    float Sc[D / 16][4];
+    float Sc[M][4];
 #pragma unroll
-    for (int m = 0; m < D / 16; ++m)
+    for (int m = 0; m < M; ++m)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const int i = 16 * m + 4 * part + c;
+            const int i = 4 * (DR_LPC * m + part) + c;
             Sc[m][c] = (i < d && live) ? Sg[(size_t)i * dv + j] : 0.f;
         }
     for (int idx = tid; idx < 2 * STAGE; idx += 128) sm[idx] = 0.f;       // the padded channels stay zero
@@ -162,8 +166,8 @@ delta_scan_kernel(const float *__restrict__ qn, const float *__restrict__ kn, co
             }
         }
         for (int idx = tid; idx < DR_TC * 32; idx += 128) {
-            const int c = idx / 32, jj = idx % 32, t = tb + c, col = blockIdx.x * 32 + jj;
-            if (t < t1 && col < dv) dr_cp_async(sv + c * 32 + jj, act + (size_t)t * C + col_v + (size_t)h * dv + col, false);
+            const int c = idx / 32, jj = idx % 32, t = tb + c, col = blockIdx.x * DR_COLS + jj;
+            if (t < t1 && jj < DR_COLS && col < dv) dr_cp_async(sv + c * 32 + jj, act + (size_t)t * C + col_v + (size_t)h * dv + col, false);
         }
         if (tid < DR_TC && tb + tid < t1) dr_cp_async(sb + tid, beta + (size_t)(tb + tid) * H + h, false);
     };
@@ -177,34 +181,36 @@ delta_scan_kernel(const float *__restrict__ qn, const float *__restrict__ kn, co
         __syncthreads();
         const float *sk = sm + (size_t)stage * STAGE, *sq = sk + DR_TC * D, *sa = sq + DR_TC * D, *sv = sa + DR_TC * D, *sb = sv + DR_TC * 32;
         const int n = min(DR_TC, t1 - tb);
-        for (int c = 0; c < n; ++c) {
+#pragma unroll
+        for (int c = 0; c < DR_TC; ++c) {             // unrolled: the next token's operands are fetched under this token's chain
+            if (c >= n) break;
             const float4 *k4 = reinterpret_cast<const float4 *>(sk + c * D), *q4 = reinterpret_cast<const float4 *>(sq + c * D),
                          *a4 = reinterpret_cast<const float4 *>(sa + c * D);
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-            for (int m = 0; m < D / 16; ++m) {
-                const float4 kk = k4[4 * m + part], aa = a4[4 * m + part];
+            for (int m = 0; m < M; ++m) {
+                const float4 kk = k4[DR_LPC * m + part], aa = a4[DR_LPC * m + part];
                 Sc[m][0] *= aa.x; s0 = fmaf(Sc[m][0], kk.x, s0);
                 Sc[m][1] *= aa.y; s1 = fmaf(Sc[m][1], kk.y, s1);
                 Sc[m][2] *= aa.z; s2 = fmaf(Sc[m][2], kk.z, s2);
                 Sc[m][3] *= aa.w; s3 = fmaf(Sc[m][3], kk.w, s3);
             }
             float acc = (s0 + s1) + (s2 + s3);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+#pragma unroll
+            for (int sh = 1; sh < DR_LPC; sh <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sh);
             const float u = sb[c] * (sv[c * 32 + jl] - acc);
             s0 = s1 = s2 = s3 = 0.f;
 #pragma unroll
-            for (int m = 0; m < D / 16; ++m) {
-                const float4 kk = k4[4 * m + part], qq = q4[4 * m + part];
+            for (int m = 0; m < M; ++m) {
+                const float4 kk = k4[DR_LPC * m + part], qq = q4[DR_LPC * m + part];
                 Sc[m][0] = fmaf(kk.x, u, Sc[m][0]); s0 = fmaf(Sc[m][0], qq.x, s0);
                 Sc[m][1] = fmaf(kk.y, u, Sc[m][1]); s1 = fmaf(Sc[m][1], qq.y, s1);
                 Sc[m][2] = fmaf(kk.z, u, Sc[m][2]); s2 = fmaf(Sc[m][2], qq.z, s2);
                 Sc[m][3] = fmaf(kk.w, u, Sc[m][3]); s3 = fmaf(Sc[m][3], qq.w, s3);
             }
             float o = (s0 + s1) + (s2 + s3);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+            for (int sh = 1; sh < DR_LPC; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
             if (live && part == 0) out[((size_t)(tb + c) * H + h) * dv + j] = o;
         }
         __syncthreads();                              // the stage may be filled again
@@ -212,10 +218,10 @@ delta_scan_kernel(const float *__restrict__ qn, const float *__restrict__ kn, co
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (live) {
 #pragma unroll
-        for (int m = 0; m < D / 16; ++m)
+        for (int m = 0; m < M; ++m)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int i = 16 * m + 4 * part + c;
+                const int i = 4 * (DR_LPC * m + part) + c;
                 if (i < d) Sg[(size_t)i * dv + j] = Sc[m][c];
             }
     }
@@ -272,7 +278,7 @@ KESTREL_API int kestrel_delta_scan(const float *qn, const float *kn, const float
     KESTREL_REQUIRE(nseq > 0 && H > 0 && G > 0 && H % G == 0 && d > 0 && dv > 0, "delta_scan: bad sizes");
     KESTREL_REQUIRE(d <= 256, "delta_scan: key size %d exceeds 256", d);
     KESTREL_REQUIRE(H <= 65535 && nseq <= 65535, "delta_scan: grid too large");
-    dim3 grid((dv + 31) / 32, H, nseq);
+    dim3 grid((dv + DR_COLS - 1) / DR_COLS, H, nseq);
 #define DR_LAUNCH(D)                                                                                                                  \
     if ((size_t)2 * (DR_TC * (3 * D + 32) + DR_TC) * sizeof(float) > 48 * 1024) {                                                      \
         static bool attr_set = false;                                                                                                 \

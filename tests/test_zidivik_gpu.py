@@ -229,7 +229,7 @@ def test_delta_rule_long_decoding():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("E,top,ff,limit,n", [(6, 2, 40, 1.0, 75), (3, 1, 24, 2.5, 9), (5, 5, 16, 0.75, 33), (40, 4, 72, 1.5, 300), (2, 1, 8, 100.0, 1)])
+@pytest.mark.parametrize("E,top,ff,limit,n", [(6, 2, 40, 1.0, 75), (3, 1, 24, 2.5, 9), (5, 5, 16, 0.75, 33), (40, 4, 72, 1.75, 300), (2, 1, 8, 100.0, 1)])
 def test_routed_experts_alone(dtype, E, top, ff, limit, n):
     import torch
     from kestrel_llm_b200.parts import RoutedExperts

@@ -48,8 +48,8 @@ Z1 = {"architecture": "Zidivik", "vocab": 211, "width": 64, "norm": {"eps": 1e-5
 # Z2: a delta layer first, a width that is no multiple of 8, no token input, attention over all keys, kept tokens beyond
 # the window's length, one tap, ranks of the low-rank projections that differ.
 Z2 = {"architecture": "Zidivik", "vocab": 97, "width": 70, "norm": {"eps": 1e-6}, "layers": [
-    layer(delta(3, 1, 24, 20, 1), moe(4, 2, 30, 1.5)),
-    layer(attn(5, 5, 14, 14, 0.5), moe(4, 1, 30, 1.5)),
+    layer(delta(3, 1, 24, 20, 1), moe(4, 2, 30, 1.25)),
+    layer(attn(5, 5, 14, 14, 0.5), moe(4, 1, 30, 2.0)),
     layer(attn(6, 3, 8, 40, 0.7, size=16, keep_first=33), moe(7, 3, 18, 3.0)),
     layer(attn(6, 3, 8, 40, 0.9, size=50, keep_first=2, kv_from=2), moe(2, 2, 50, 1.0)),
     layer(delta(6, 2, 64, 32, 5), None),
