@@ -399,3 +399,70 @@ def test_greedy_generation_through_the_scheduler(zdirs, dtype):
                 gap = float(logits[want] - logits[got])
                 assert gap <= (2e-5 if dtype == "float32" else 4e-2) * float(np.abs(logits).max()), f"{dtype}: token {got} instead of {want}"
             toks.append(got)
+
+
+# ---- the programs a user runs ------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype,graphs", [("float32", 1), ("bfloat16", 1), ("bfloat16", 0)])
+def test_trace_replay_program(zdirs, dtype, graphs, tmp_path):
+    """bin/trace_run in a process of its own on a mixed trace: four state slots for seven requests, decode steps replayed
+    from captured graphs (the default) and launched kernel by kernel."""
+    import json
+    import os
+    import subprocess
+    import sys
+    name = "Z1"
+    reqs = R.random_requests(Z.CONFIGS[name][0]["vocab"], (5, 33, 70, 47, 90, 16, 65), seed=21)
+    steps, max_tokens = R.trace_mixed(reqs, live_max=4, seed=5)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lines = "".join(json.dumps(dict(step=i, **s)) + "\n" for i, s in enumerate(steps))
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", zdirs[name][dtype], "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", str(max_tokens), "--cuda-graphs", str(graphs)], input=lines, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+    V = Z.CONFIGS[name][0]["vocab"]
+    pos = {n: 0 for n in reqs}
+    got = {n: {} for n in reqs}
+    for i, s in enumerate(steps):
+        arr = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+        r = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                got[e["id"]][pos[e["id"]] + w] = arr[r]
+                r += 1
+            pos[e["id"]] += len(e["tokens"])
+        assert r == arr.shape[0]
+    Z.compare_with_plain(zdirs[name]["float32"], reqs, got, dtype, f"trace_run/{dtype}")
+
+
+def test_command_line_writes_random_weights_and_generates(tmp_path):
+    """bin/kestrel: `--random-weights` writes a Zidivik folder from a config.json with the design's own keys (the ranks of
+    the low-rank projections named in it), and the streaming harness prints the plain implementation's greedy tokens."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    raw = json.loads(json.dumps(Z.Z1))
+    for L in raw["layers"]:
+        if L["type"] == "channel_delta":
+            L["mixer"].update(decay_rank=6, gate_rank=10)
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(raw))
+    model_dir = tmp_path / "written"
+    prompt = R.random_requests(raw["vocab"], (23,), seed=2)["r0"]
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "kestrel"), "--model", str(model_dir), "--config", str(cfg_file),
+                        "--random-weights", "5", "--dtype", "float32", "--stream-test", "--stream-n", "8", "--prompt-ids",
+                        ",".join(str(t) for t in prompt), "--ignore-eos", "--max-tokens", "256", "--batch-max", "2"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("[STREAM] TOKIDS:")]
+    assert len(line) == 1
+    pcfg, W = P.read_model(str(model_dir))
+    assert W["l1.mix.a1"].shape[0] == 6 and W["l1.mix.g1"].shape[0] == 10
+    toks, want = list(prompt), []
+    for _ in range(8):
+        want.append(P.greedy(P.forward(pcfg, W, toks)[-1]))
+        toks.append(want[-1])
+    assert [int(t) for t in line[0].split(":")[1].split()] == want
