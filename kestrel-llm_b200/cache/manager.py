@@ -252,7 +252,12 @@ class CacheManager(PageTable):
                 # of a captured step write their keys and values
                 shape = (num_pages + 1, sp.kv_heads, page_size, sp.head_dim)
                 self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-                self.v.append(torch.zeros(shape[:3] + (sp.value_dim,), dtype=dtype, device=device))
+                if sp.values_are_keys:
+                    if sp.value_dim != sp.head_dim:
+                        raise CacheError("a layer whose values are its keys has one size for both")
+                    self.v.append(self.k[-1])
+                else:
+                    self.v.append(torch.zeros(shape[:3] + (sp.value_dim,), dtype=dtype, device=device))
                 self.state.append(None)
             elif isinstance(sp, FixedStateSpec):
                 self.k.append(None)
@@ -291,5 +296,5 @@ class CacheManager(PageTable):
         n = 0
         for sp in self.specs:
             if isinstance(sp, PagedKVSpec):
-                n += sp.kv_heads * (sp.head_dim + sp.value_dim) * torch.empty((), dtype=self.dtype).element_size()
+                n += sp.kv_heads * (sp.head_dim + (0 if sp.values_are_keys else sp.value_dim)) * torch.empty((), dtype=self.dtype).element_size()
         return n

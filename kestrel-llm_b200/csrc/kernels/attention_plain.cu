@@ -17,7 +17,13 @@
 // keys are then positions 0..min(keep_first, lo)-1 followed by lo..p, walked in this order);
 // values may have a size `vd` of their own (the V planes are [page][kv_head][slot][vd]); and
 // `gate`, float32 [T, nq], multiplies each head's output.
+//
+// A layer may also change the scores and the way keys are weighed (`ScoreOpts`, attention_score.cuh):
+// a cap, a logarithmic distance term, a softmax with a valueless extra term exp(0) in its
+// denominator - it enters the merge as one more state (max 0, sum 1, out 0) in front of the warps'
+// - or sigmoid weights that are not normalised, where the states are plain sums.
 #include "common.cuh"
+#include "attention_score.cuh"
 #include <math.h>
 
 #define PA_WARPS 4
@@ -30,7 +36,7 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
                        const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                        const int *__restrict__ block_table, int table_stride, int page_size,
                        T *__restrict__ out, int nq, int nkv, int hd, int vd, int window, int keep_first,
-                       const float *__restrict__ gate, float scale) {
+                       const float *__restrict__ gate, float scale, const ScoreOpts opts) {
     pdl_launch_dependents();
     pdl_wait();
     int t = blockIdx.x, h = blockIdx.y;
@@ -52,6 +58,8 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
         acc[c] = 0.f;
     }
     float m = -INFINITY, l = 0.f;
+    const HeadScore score(opts, h);
+    const bool sigmoid = opts.weighting == KESTREL_WEIGH_SIGMOID;
 
     for (int base = warp * PA_KEYS; base < n_keys; base += PA_WARPS * PA_KEYS) {
         float sc[PA_KEYS];
@@ -74,7 +82,21 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
                 }
             }
             dot = warp_sum(dot);
-            sc[u] = (j < n_keys) ? dot * scale : -INFINITY;
+            sc[u] = (j < n_keys) ? score(dot * scale, pos - s) : -INFINITY;
+        }
+        if (sigmoid) {                      // no running maximum: the weights are sums as they are
+#pragma unroll
+            for (int u = 0; u < PA_KEYS; ++u) {
+                if (vrow[u]) {
+                    const float p = sigmoid_f32(sc[u]);
+#pragma unroll
+                    for (int c = 0; c < PA_MAX_PER_LANE; ++c) {
+                        int i = lane + 32 * c;
+                        if (c < per_lane_v && i < vd) acc[c] = fmaf(p, to_f32<T>(vrow[u][i]), acc[c]);
+                    }
+                }
+            }
+            continue;
         }
         float mn = m;
 #pragma unroll
@@ -106,22 +128,28 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
     for (int c = 0; c < PA_MAX_PER_LANE; ++c) sm_acc[warp][lane + 32 * c] = acc[c];
     __syncthreads();
     if (warp == 0) {
-        float M = -INFINITY;
+        const bool sink = opts.weighting == KESTREL_WEIGH_SOFTMAX_SINK;
+        float M = sink ? 0.f : -INFINITY;
 #pragma unroll
         for (int w = 0; w < PA_WARPS; ++w) M = fmaxf(M, sm_m[w]);
-        float L = 0.f;
+        float L = sink ? expf(0.f - M) : 0.f;
         float o[PA_MAX_PER_LANE];
 #pragma unroll
         for (int c = 0; c < PA_MAX_PER_LANE; ++c) o[c] = 0.f;
 #pragma unroll
         for (int w = 0; w < PA_WARPS; ++w) {
+            if (sigmoid) {
+#pragma unroll
+                for (int c = 0; c < PA_MAX_PER_LANE; ++c) o[c] += sm_acc[w][lane + 32 * c];
+                continue;
+            }
             if (sm_m[w] == -INFINITY) continue;     // a warp that saw no key
             float f = expf(sm_m[w] - M);
             L += sm_l[w] * f;
 #pragma unroll
             for (int c = 0; c < PA_MAX_PER_LANE; ++c) o[c] += sm_acc[w][lane + 32 * c] * f;
         }
-        float inv = 1.0f / L;
+        float inv = sigmoid ? 1.0f : 1.0f / L;
         if (gate) inv *= gate[(size_t)t * nq + h];
         T *orow = out + ((size_t)t * nq + h) * vd;
 #pragma unroll
@@ -132,25 +160,38 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
     }
 }
 
-KESTREL_API int kestrel_attention_plain_ex(const void *q, const void *k_cache, const void *v_cache,
-                                           const int *positions, const int *seq_of_token,
-                                           const int *block_table, int table_stride, int page_size,
-                                           void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window,
-                                           int keep_first, const float *gate, float scale, cudaStream_t stream) {
+KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cache, const void *v_cache,
+                                               const int *positions, const int *seq_of_token,
+                                               const int *block_table, int table_stride, int page_size,
+                                               void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window,
+                                               int keep_first, const float *gate, float scale, float softcap, const float *r1,
+                                               const float *r2, const float *head_bias, int weighting, cudaStream_t stream) {
     if (T == 0) return 0;
+    KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_plain: bad score options");
+    const ScoreOpts opts = {softcap, r1, r2, head_bias, weighting};
     KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0 && vd > 0 && keep_first >= 0, "attention_plain: bad sizes");
     KESTREL_REQUIRE(hd <= 32 * PA_MAX_PER_LANE && vd <= 32 * PA_MAX_PER_LANE, "attention_plain: head size %d / %d exceeds %d", hd, vd, 32 * PA_MAX_PER_LANE);
     KESTREL_REQUIRE(nq <= 65535, "attention_plain: %d query heads exceed the grid", nq);
     dim3 grid(T, nq);
     if (dtype == KESTREL_F32)
         kestrel_launch(attention_plain_kernel<float>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const float *)q, (const float *)k_cache, (const float *)v_cache, positions, seq_of_token,
-            block_table, table_stride, page_size, (float *)out, nq, nkv, hd, vd, window, keep_first, gate, scale);
+            block_table, table_stride, page_size, (float *)out, nq, nkv, hd, vd, window, keep_first, gate, scale, opts);
     else if (dtype == KESTREL_BF16)
         kestrel_launch(attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, positions,
-            seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)out, nq, nkv, hd, vd, window, keep_first, gate, scale);
+            seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)out, nq, nkv, hd, vd, window, keep_first, gate, scale, opts);
     else
         return kestrel_fail(-2, "attention_plain: unknown dtype %d", dtype);
     return kestrel_check_launch("attention_plain");
+}
+
+KESTREL_API int kestrel_attention_plain_ex(const void *q, const void *k_cache, const void *v_cache,
+                                           const int *positions, const int *seq_of_token,
+                                           const int *block_table, int table_stride, int page_size,
+                                           void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window,
+                                           int keep_first, const float *gate, float scale, cudaStream_t stream) {
+    return kestrel_attention_plain_scored(q, k_cache, v_cache, positions, seq_of_token, block_table, table_stride, page_size, out, dtype, T,
+                                          nq, nkv, hd, vd, window, keep_first, gate, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX,
+                                          stream);
 }
 
 KESTREL_API int kestrel_attention_plain(const void *q, const void *k_cache, const void *v_cache,

@@ -4,13 +4,17 @@
 // The product's columns are [ q: nq*hd | k: nkv*hd | v: nkv*vd | gate: nq ]; the k and v parts are
 // absent (`has_kv` = 0) in a layer that attends over another layer's cache, the gate part where
 // `gate_out` is null.  Per token:
-//   q, k  <- x / sqrt(mean(x^2) + eps) per head, times a weight [hd] where one is given
-//            (`qk_norm` = 0 leaves them as they are);
+//   every column gets its entry of `bias` (float32, indexed like the product's columns) if one is given;
+//   `qk_norm` = 1: q, k <- x / sqrt(mean(x^2) + eps) per head, times a weight [hd] where one is given;
+//   `qk_norm` = 2: the same over the whole q projection (all nq * hd columns at once) and the whole k
+//            projection, with weights [nq * hd] and [nkv * hd]; `qk_norm` = 0 leaves them as they are;
+//   `v_norm`: v <- v / sqrt(mean(v^2) + eps) per head, no weight (it is cached so);
 //   q -> q_out in the storage type; k, v -> the token's slot in its request's pages;
 //   gate_out[t, h] = sigmoid(gate column h), float32.
 // One warp a head row (the blocks of a token share its head rows out), lanes over the head's
 // entries, sums of squares in float32 in a fixed shuffle tree: a token's result does not depend on
-// the batch.
+// the batch.  For the norm over a whole projection every block first sums the squares of each q and
+// k head (a warp a head, as above) into shared memory and adds the heads' sums in ascending order.
 #include "common.cuh"
 #include <math.h>
 
@@ -24,12 +28,37 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
                        const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                        const int *__restrict__ block_table, int table_stride, int page_size,
                        T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out, float *__restrict__ gate_out,
-                       int nq, int nkv, int hd, int vd, int has_kv) {
+                       int nq, int nkv, int hd, int vd, int has_kv, const float *__restrict__ bias, int v_norm) {
+    extern __shared__ float apx_ss[];              // qk_norm = 2: sum of squares of every q and k head
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float *row = partial + (size_t)t * ld;
     const int n_heads = nq + (has_kv ? 2 * nkv : 0);
+    float mul_q = 1.f, mul_k = 1.f;
+    if (qk_norm == 2) {
+        const int n_qk = nq + (has_kv ? nkv : 0);
+        for (int r = warp; r < n_qk; r += APX_WARPS) {
+            float ss = 0.f;
+#pragma unroll
+            for (int c = 0; c < APX_PER_LANE; ++c) {
+                const int i = lane + 32 * c;
+                if (i < hd) {
+                    float v = sum_slices(row, S, slice_stride, r * hd + i);
+                    if (bias) v += bias[r * hd + i];
+                    ss = fmaf(v, v, ss);
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) apx_ss[r] = ss;
+        }
+        __syncthreads();
+        float tq = 0.f, tk = 0.f;
+        for (int r = 0; r < nq; ++r) tq += apx_ss[r];
+        for (int r = nq; r < n_qk; ++r) tk += apx_ss[r];
+        mul_q = 1.0f / sqrtf(tq / (float)(nq * hd) + eps);
+        mul_k = 1.0f / sqrtf(tk / (float)(nkv * hd) + eps);
+    }
     size_t slot_row = 0;
     if (has_kv) {
         const int pos = positions[t];
@@ -47,16 +76,23 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
 #pragma unroll
         for (int c = 0; c < APX_PER_LANE; ++c) {
             const int i = lane + 32 * c;
-            const float v = i < n ? sum_slices(row, S, slice_stride, col0 + i) : 0.f;
+            float v = i < n ? sum_slices(row, S, slice_stride, col0 + i) : 0.f;
+            if (bias && i < n) v += bias[col0 + i];
             x[c] = v;
             ss = fmaf(v, v, ss);
         }
         float mul = 1.f;
         const float *w = nullptr;
-        if (kind != 2 && qk_norm) {
+        if (kind != 2 && qk_norm == 1) {
             ss = warp_sum(ss);
             mul = 1.0f / sqrtf(ss / (float)n + eps);
             w = kind == 0 ? q_w : k_w;
+        } else if (kind != 2 && qk_norm == 2) {
+            mul = kind == 0 ? mul_q : mul_k;
+            w = (kind == 0 ? q_w : k_w) + (size_t)head * hd;       // a weight per column of the projection
+        } else if (kind == 2 && v_norm) {
+            ss = warp_sum(ss);
+            mul = 1.0f / sqrtf(ss / (float)n + eps);
         }
         T *dst = kind == 0 ? q_out + ((size_t)t * nq + head) * hd
                            : (kind == 1 ? k_cache + (slot_row + (size_t)head * page_size) * hd
@@ -70,18 +106,23 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
     if (gate_out && blockIdx.y == 0) {
         const int col0 = nq * hd + (has_kv ? nkv * (hd + vd) : 0);
         for (int h = threadIdx.x; h < nq; h += APX_WARPS * 32) {
-            const float z = sum_slices(row, S, slice_stride, col0 + h);
+            float z = sum_slices(row, S, slice_stride, col0 + h);
+            if (bias) z += bias[col0 + h];
             gate_out[(size_t)t * nq + h] = 1.0f / (1.0f + expf(-z));
         }
     }
 }
 
-KESTREL_API int kestrel_attn_prepare_ex(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w,
-                                        const float *k_norm_w, int qk_norm, float norm_eps, const int *positions,
-                                        const int *seq_of_token, const int *block_table, int table_stride, int page_size,
-                                        void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq,
-                                        int nkv, int hd, int vd, int has_kv, cudaStream_t stream) {
+KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w,
+                                            const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const int *positions,
+                                            const int *seq_of_token, const int *block_table, int table_stride, int page_size,
+                                            void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq,
+                                            int nkv, int hd, int vd, int has_kv, cudaStream_t stream) {
     if (T == 0) return 0;
+    KESTREL_REQUIRE(qk_norm >= 0 && qk_norm <= 2, "attn_prepare_ex: qk_norm %d is none of 0, 1, 2", qk_norm);
+    KESTREL_REQUIRE(qk_norm != 2 || (q_norm_w && (k_norm_w || !has_kv)), "attn_prepare_ex: the norm over a whole projection needs its weights");
+    const size_t smem = qk_norm == 2 ? (size_t)(nq + nkv) * sizeof(float) : 0;
+    KESTREL_REQUIRE(smem <= 40000, "attn_prepare_ex: %d heads exceed the shared memory of the norm over a whole projection", nq + nkv);
     KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0 && vd > 0 && S > 0, "attn_prepare_ex: bad sizes");
     KESTREL_REQUIRE(hd <= 32 * APX_PER_LANE && vd <= 32 * APX_PER_LANE, "attn_prepare_ex: head size %d / %d exceeds %d", hd, vd, 32 * APX_PER_LANE);
     const int need = nq * hd + (has_kv ? nkv * (hd + vd) : 0) + (gate_out ? nq : 0);
@@ -90,13 +131,23 @@ KESTREL_API int kestrel_attn_prepare_ex(const float *partial, int S, long long s
     const int n_heads = nq + (has_kv ? 2 * nkv : 0);
     const int by = T >= 512 ? 1 : (n_heads + APX_WARPS - 1) / APX_WARPS;
     if (dtype == KESTREL_F32)
-        kestrel_launch(attn_prepare_ex_kernel<float>, dim3(T, by), dim3(APX_WARPS * 32), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
-                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv);
+        kestrel_launch(attn_prepare_ex_kernel<float>, dim3(T, by), dim3(APX_WARPS * 32), smem, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
+                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv, bias, v_norm);
     else if (dtype == KESTREL_BF16)
-        kestrel_launch(attn_prepare_ex_kernel<__nv_bfloat16>, dim3(T, by), dim3(APX_WARPS * 32), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
+        kestrel_launch(attn_prepare_ex_kernel<__nv_bfloat16>, dim3(T, by), dim3(APX_WARPS * 32), smem, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, gate_out, nq, nkv,
-                       hd, vd, has_kv);
+                       hd, vd, has_kv, bias, v_norm);
     else
         return kestrel_fail(-2, "attn_prepare_ex: unknown dtype %d", dtype);
     return kestrel_check_launch("attn_prepare_ex");
+}
+
+KESTREL_API int kestrel_attn_prepare_ex(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w,
+                                        const float *k_norm_w, int qk_norm, float norm_eps, const int *positions,
+                                        const int *seq_of_token, const int *block_table, int table_stride, int page_size,
+                                        void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq,
+                                        int nkv, int hd, int vd, int has_kv, cudaStream_t stream) {
+    return kestrel_attn_prepare_normed(partial, S, slice_stride, ld, nullptr, q_norm_w, k_norm_w, qk_norm ? 1 : 0, 0, norm_eps, positions,
+                                       seq_of_token, block_table, table_stride, page_size, k_cache, v_cache, q_out, gate_out, dtype, T,
+                                       nq, nkv, hd, vd, has_kv, stream);
 }

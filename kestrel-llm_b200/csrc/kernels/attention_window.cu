@@ -21,10 +21,17 @@
 // the longest request's row tiles for every request; CTAs beyond a request's rows leave at once,
 // so nothing of the step is read on the host and a launch can be recorded for replay.
 //
+// A layer may change the scores and the weighing of keys (`ScoreOpts`, attention_score.cuh): a cap and a
+// logarithmic distance term on the float32 scores; a softmax whose denominator has a valueless extra
+// term exp(0), added where a row's states are closed; or sigmoid weights that are not normalised,
+// which need no running maximum - P is the weights themselves.  Without options the scores keep the
+// short path (one multiply into the exponent's base-2 scale).
+//
 // Head sizes in multiples of 8 up to 256; the kernel is instantiated for 32, 64, 128 and 256 and
 // smaller heads are padded with zero columns in shared memory.
 #include "common.cuh"
 #include "mma_sync.cuh"
+#include "attention_score.cuh"
 #include <math.h>
 
 #define AW_THREADS 128
@@ -39,7 +46,9 @@ struct AwParams {
     const float *gate;              // [T, nq] or null
     const int *cu_seqlens, *kv_lens, *block_table;
     int table_stride, page_size, nq, nkv, hd, vd, window, keep_first;
-    float scale_log2;
+    float scale_log2, scale;
+    ScoreOpts opts;
+    int scored;                     // any of the options is on
 };
 
 __device__ __forceinline__ void aw_cp_async16(uint32_t dst, const void *src, bool valid) {
@@ -119,6 +128,10 @@ attention_window_kernel(const AwParams p) {
         const int r = rt * 16 + g + 8 * h2;
         pos_r[h2] = r < rows_here ? pos_begin + (row0 + r) / G : -1;
     }
+    const bool sigmoid = p.opts.weighting == KESTREL_WEIGH_SIGMOID, sink = p.opts.weighting == KESTREL_WEIGH_SOFTMAX_SINK;
+    ScoreOpts no_opts = {0.f, nullptr, nullptr, nullptr, 0};
+    const HeadScore hs[2] = {HeadScore(p.scored ? p.opts : no_opts, kvh * G + (row0 + min(rt * 16 + g, rows_here - 1)) % G),
+                             HeadScore(p.scored ? p.opts : no_opts, kvh * G + (row0 + min(rt * 16 + g + 8, rows_here - 1)) % G)};
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
     float o[D / 8][4];
 #pragma unroll
@@ -162,15 +175,46 @@ attention_window_kernel(const AwParams p) {
             }
             // mask, scale, running maximum
             float mx[2] = {-INFINITY, -INFINITY};
+            if (!p.scored) {
 #pragma unroll
-            for (int j = 0; j < AW_BN / 8; ++j)
+                for (int j = 0; j < AW_BN / 8; ++j)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int s = s0 + j * 8 + 2 * tq + (c & 1), pr = pos_r[c >> 1];
-                    const bool ok = s >= lo && s < up && s <= pr && (p.window <= 0 || pr - s < p.window || s < p.keep_first);
-                    sc[j][c] = ok ? sc[j][c] * p.scale_log2 : -INFINITY;
-                    mx[c >> 1] = fmaxf(mx[c >> 1], sc[j][c]);
+                    for (int c = 0; c < 4; ++c) {
+                        const int s = s0 + j * 8 + 2 * tq + (c & 1), pr = pos_r[c >> 1];
+                        const bool ok = s >= lo && s < up && s <= pr && (p.window <= 0 || pr - s < p.window || s < p.keep_first);
+                        sc[j][c] = ok ? sc[j][c] * p.scale_log2 : -INFINITY;
+                        mx[c >> 1] = fmaxf(mx[c >> 1], sc[j][c]);
+                    }
+            } else {
+#pragma unroll
+                for (int j = 0; j < AW_BN / 8; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int s = s0 + j * 8 + 2 * tq + (c & 1), pr = pos_r[c >> 1];
+                        const bool ok = s >= lo && s < up && s <= pr && (p.window <= 0 || pr - s < p.window || s < p.keep_first);
+                        const float z = ok ? hs[c >> 1](sc[j][c] * p.scale, pr - s) : 0.f;
+                        if (sigmoid) sc[j][c] = ok ? sigmoid_f32(z) : 0.f;            // the weight itself
+                        else sc[j][c] = ok ? z * 1.4426950408889634f : -INFINITY;
+                        mx[c >> 1] = fmaxf(mx[c >> 1], sc[j][c]);
+                    }
+            }
+            if (sigmoid) {
+#pragma unroll
+                for (int k2 = 0; k2 < AW_BN / 16; ++k2) {
+                    uint32_t a[4] = {pack_bf16(sc[2 * k2][0], sc[2 * k2][1]), pack_bf16(sc[2 * k2][2], sc[2 * k2][3]),
+                                     pack_bf16(sc[2 * k2 + 1][0], sc[2 * k2 + 1][1]), pack_bf16(sc[2 * k2 + 1][2], sc[2 * k2 + 1][3])};
+#pragma unroll
+                    for (int np = 0; np < D / 16; ++np) {
+                        if (np < v_pairs) {
+                            uint32_t b0, b1, b2, b3;
+                            ldmatrix_x4_trans((uint32_t)__cvta_generic_to_shared(Vg + (k2 * 16 + v_row) * LDS + np * 16 + v_col), b0, b1, b2, b3);
+                            mma_bf16(o[2 * np], a, b0, b1);
+                            mma_bf16(o[2 * np + 1], a, b2, b3);
+                        }
+                    }
                 }
+                continue;
+            }
             float corr[2], ms[2];
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
@@ -224,6 +268,11 @@ attention_window_kernel(const AwParams p) {
             if (r >= rows_here) continue;
             const int row = row0 + r, tok = tok_begin + row / G, head = kvh * G + row % G;
             float inv = 1.0f / l_r[h2];
+            if (sigmoid) inv = 1.0f;
+            if (sink) {                                   // one more state in front: maximum 0, sum 1, no value
+                const float M = fmaxf(m_r[h2], 0.f), f = fast_exp2(m_r[h2] - M);
+                inv = f / (fast_exp2(0.f - M) + l_r[h2] * f);
+            }
             if (p.gate) inv *= p.gate[(size_t)tok * p.nq + head];
             __nv_bfloat16 *dst = p.out + ((size_t)tok * p.nq + head) * vd;
 #pragma unroll
@@ -250,19 +299,20 @@ attention_window_kernel(const AwParams p) {
         __syncthreads();
         for (int idx = tid; idx < rows_here * vd; idx += AW_THREADS) {
             const int r = idx / vd, col = idx % vd;
-            float M = -INFINITY;
+            float M = sink ? 0.f : -INFINITY;
 #pragma unroll
             for (int w = 0; w < KW; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
-            float L = 0.f, acc = 0.f;
+            float L = sink ? fast_exp2(0.f - M) : 0.f, acc = 0.f;
 #pragma unroll
             for (int w = 0; w < KW; ++w) {
+                if (sigmoid) { acc += sm_o[((size_t)w * 16 + r) * D + col]; continue; }
                 if (sm_m[w * 16 + r] == -INFINITY) continue;
                 const float f = fast_exp2(sm_m[w * 16 + r] - M);
                 L += sm_l[w * 16 + r] * f;
                 acc += sm_o[((size_t)w * 16 + r) * D + col] * f;
             }
             const int row = row0 + r, tok = tok_begin + row / G, head = kvh * G + row % G;
-            float v = acc / L;
+            float v = sigmoid ? acc : acc / L;
             if (p.gate) v *= p.gate[(size_t)tok * p.nq + head];
             p.out[((size_t)tok * p.nq + head) * vd + col] = __float2bfloat16_rn(v);
         }
@@ -295,7 +345,17 @@ KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, con
                                          const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size,
                                          int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
                                          cudaStream_t stream) {
+    return kestrel_attention_window_scored(q, k_cache, v_cache, out, gate, cu_seqlens, kv_lens, block_table, table_stride, page_size, nseq, max_count,
+                                           nq, nkv, hd, vd, window, keep_first, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, stream);
+}
+
+KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate,
+                                                const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size,
+                                                int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
+                                                float softcap, const float *r1, const float *r2, const float *head_bias, int weighting,
+                                                cudaStream_t stream) {
     if (nseq == 0 || max_count == 0) return 0;
+    KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_window: bad score options");
     KESTREL_REQUIRE(kestrel_attention_window_supported(hd, vd, nq, nkv), "attention_window: head sizes %d / %d, heads %d / %d are not taken", hd, vd, nq, nkv);
     KESTREL_REQUIRE(nseq > 0 && nseq <= 65535 && nkv <= 65535 && max_count > 0 && window >= 0 && keep_first >= 0, "attention_window: bad sizes");
     AwParams p;
@@ -316,6 +376,9 @@ KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, con
     p.window = window;
     p.keep_first = window > 0 ? keep_first : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.scale = scale;
+    p.opts = {softcap, r1, r2, head_bias, weighting};
+    p.scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     const int D = max(hd, vd), G = nq / nkv;
     const bool keys_mode = (long long)max_count * G <= 16;
 #define AW_CASE(DD)                                                                   \

@@ -793,36 +793,89 @@ def partial_columns(p: Partials, col0: int, n: int, dtype: torch.dtype) -> torch
 
 # ---- attention without rotation, values of their own size, kept first tokens, an output gate -----
 
-def attn_prepare_ex(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], qk_norm: bool, norm_eps: float,
+QK_NORM_MODES = {None: 0, False: 0, "none": 0, True: 1, "head": 1, "projection": 2}
+
+
+def attn_prepare_ex(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], qk_norm, norm_eps: float,
                     positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
                     k_cache: torch.Tensor, v_cache: torch.Tensor, q_out: torch.Tensor, gate_out: Optional[torch.Tensor],
-                    nq: int, nkv: int, hd: int, vd: int, has_kv: bool) -> None:
-    """Columns [q | k | v | gate] of a fused product: q and k divided by their root mean square per
-    head (times a weight where given), q to ``q_out``, k and v into the cache pages (absent if
-    ``has_kv`` is False), sigmoid of the gate columns to ``gate_out`` float32 [T, nq]."""
+                    nq: int, nkv: int, hd: int, vd: int, has_kv: bool, v_norm: bool = False) -> None:
+    """Columns [q | k | v | gate] of a fused product, plus the product's bias where it carries one:
+    q and k divided by their root mean square - ``qk_norm`` "head" (or True): per head, times a
+    weight [hd] where given; "projection": over all of q's columns at once and all of k's, times
+    weights [nq hd] and [nkv hd]; None: left as they are - and v per head if ``v_norm``; q to
+    ``q_out``, k and v into the cache pages (absent if ``has_kv`` is False), sigmoid of the gate
+    columns to ``gate_out`` float32 [T, nq]."""
     _need(q_out, "attn_prepare_ex.q_out", dims=2)
     _need(block_table, "attn_prepare_ex.block_table", torch.int32, 2)
     _need(k_cache, "attn_prepare_ex.k_cache", q_out.dtype, 4)
     _need(v_cache, "attn_prepare_ex.v_cache", q_out.dtype, 4)
     T = q_out.shape[0]
-    if qkv.tokens != T or q_out.shape[1] != nq * hd or qkv.bias is not None:
+    if qkv.tokens != T or q_out.shape[1] != nq * hd:
         raise KernelError("attn_prepare_ex: shapes differ")
+    if qk_norm not in QK_NORM_MODES:
+        raise KernelError(f"attn_prepare_ex: qk_norm {qk_norm!r} is none of None, 'head', 'projection'")
+    mode = QK_NORM_MODES[qk_norm]
+    if qkv.bias is not None:
+        _need(qkv.bias, "attn_prepare_ex.bias", torch.float32, 1)
+        if qkv.bias.shape[0] != qkv.width:
+            raise KernelError("attn_prepare_ex: the bias does not fit the product's columns")
+    if mode == 2:
+        for w, n, name in ((q_norm_w, nq * hd, "q"), (k_norm_w, nkv * hd, "k")):
+            if (w is None and (name == "q" or has_kv)) or (w is not None and (w.dtype != torch.float32 or w.numel() != n)):
+                raise KernelError(f"attn_prepare_ex: the norm over the whole {name} projection needs a float32 weight of {n} entries")
     if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, vd):
         raise KernelError("attn_prepare_ex: the cache planes do not fit the heads")
     if gate_out is not None:
         _need(gate_out, "attn_prepare_ex.gate_out", torch.float32, 2)
-    _check(library().kestrel_attn_prepare_ex(
-        qkv.data.data_ptr(), qkv.slices, qkv.slice_stride, qkv.width, _p(q_norm_w), _p(k_norm_w), 1 if qk_norm else 0, float(norm_eps),
-        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
+    _check(library().kestrel_attn_prepare_normed(
+        qkv.data.data_ptr(), qkv.slices, qkv.slice_stride, qkv.width, _p(qkv.bias), _p(q_norm_w), _p(k_norm_w), mode, 1 if v_norm else 0,
+        float(norm_eps), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
         k_cache.data_ptr(), v_cache.data_ptr(), q_out.data_ptr(), _p(gate_out), _code(q_out, "attn_prepare_ex.q_out"), T, nq, nkv, hd, vd,
         1 if has_kv else 0, _stream()))
 
 
+WEIGHTINGS = {"softmax": 0, "softmax_sink": 1, "sigmoid": 2}
+
+
+class ScoreOptions:
+    """What a layer does to its scores s = q . k * scale and how it weighs keys, all in float32:
+    ``softcap`` > 0: s <- softcap tanh(s / softcap); ``r1``, ``r2`` (float32 [heads], both or
+    neither): s <- s - r1[h] ln(1 + r2[h] (i - j)) for the key j behind the query i; ``weighting``
+    "softmax", "softmax_sink" (one more term exp(0) in the denominator, without a value) or
+    "sigmoid" (every visible key weighs sigmoid(s + head_bias[h]), nothing is normalised)."""
+
+    __slots__ = ("softcap", "r1", "r2", "head_bias", "weighting")
+
+    def __init__(self, softcap: float = 0.0, r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
+                 head_bias: Optional[torch.Tensor] = None, weighting: str = "softmax"):
+        if weighting not in WEIGHTINGS:
+            raise KernelError(f"weighting '{weighting}' is none of {', '.join(WEIGHTINGS)}")
+        if (r1 is None) != (r2 is None):
+            raise KernelError("the distance term needs both of its per-head numbers")
+        if softcap < 0:
+            raise KernelError("a score cap is positive, or 0 for none")
+        self.softcap, self.r1, self.r2, self.head_bias, self.weighting = float(softcap), r1, r2, head_bias, weighting
+
+    def args(self, nq: int):
+        for t, name in ((self.r1, "r1"), (self.r2, "r2"), (self.head_bias, "head_bias")):
+            if t is not None:
+                _need(t, f"score.{name}", torch.float32, 1)
+                if t.shape[0] != nq:
+                    raise KernelError(f"score.{name}: {t.shape[0]} entries for {nq} heads")
+        return self.softcap, _p(self.r1), _p(self.r2), _p(self.head_bias), WEIGHTINGS[self.weighting]
+
+
+_NO_SCORE = ScoreOptions()
+
+
 def attention_plain_ex(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
                        seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, out: torch.Tensor, nq: int, nkv: int,
-                       hd: int, vd: int, window: int, keep_first: int, gate: Optional[torch.Tensor], scale: float) -> None:
+                       hd: int, vd: int, window: int, keep_first: int, gate: Optional[torch.Tensor], scale: float,
+                       score: Optional[ScoreOptions] = None) -> None:
     """`attention_plain` with values of size ``vd``, the first ``keep_first`` keys of a request
-    visible beyond the window, and each head's output multiplied by ``gate`` [T, nq]."""
+    visible beyond the window, each head's output multiplied by ``gate`` [T, nq], and the layer's
+    `ScoreOptions`."""
     _need(q, "attention.q", dims=2)
     _need(out, "attention.out", q.dtype, 2)
     _need(k_cache, "attention.k_cache", q.dtype, 4)
@@ -833,10 +886,10 @@ def attention_plain_ex(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         raise KernelError("attention: shapes differ")
     if gate is not None:
         _need(gate, "attention.gate", torch.float32, 2)
-    _check(library().kestrel_attention_plain_ex(
+    _check(library().kestrel_attention_plain_scored(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), int(page_size), out.data_ptr(), _code(q, "attention.q"), T, nq, nkv, hd, vd, int(window), int(keep_first),
-        _p(gate), float(scale), _stream()))
+        _p(gate), float(scale), *(score or _NO_SCORE).args(nq), _stream()))
 
 
 def attention_window_supported(hd: int, vd: int, nq: int, nkv: int) -> bool:
@@ -846,7 +899,7 @@ def attention_window_supported(hd: int, vd: int, nq: int, nkv: int) -> bool:
 
 def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch, block_table: torch.Tensor, page_size: int,
                      out: torch.Tensor, nq: int, nkv: int, hd: int, vd: int, window: int, keep_first: int, gate: Optional[torch.Tensor],
-                     scale: float) -> None:
+                     scale: float, score: Optional[ScoreOptions] = None) -> None:
     """`attention_plain_ex` for bfloat16 on the tensor cores, over this step's requests as ``batch``
     describes them (cumulative lengths, lengths after the step and the most tokens of one request)."""
     _need(q, "attention_window.q", torch.bfloat16, 2)
@@ -861,10 +914,68 @@ def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         raise KernelError("attention_window: the cache planes do not fit the heads")
     if gate is not None:
         _need(gate, "attention_window.gate", torch.float32, 2)
-    _check(library().kestrel_attention_window(
+    _check(library().kestrel_attention_window_scored(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate), batch.cu_seqlens.data_ptr(), batch.kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), int(page_size), int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, int(window),
-        int(keep_first), float(scale), _stream()))
+        int(keep_first), float(scale), *(score or _NO_SCORE).args(nq), _stream()))
+
+
+# ---- attention over cached latents -----------------------------------------------------------
+
+def latent_prepare(fused: Partials, q_norm_w: torch.Tensor, kv_norm_w: torch.Tensor, norm_eps: float, positions: torch.Tensor,
+                   seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, latent_cache: torch.Tensor, q_out: torch.Tensor,
+                   gate_out: Optional[torch.Tensor]) -> None:
+    """Columns [query latent | key/value latent | gate] of a fused product: both latents RMS-normed
+    with their weights; the query latent to ``q_out`` [T, q_rank], the key/value latent into the
+    token's slot of ``latent_cache`` [pages, 1, page size, kv_rank], sigmoid of the gate columns to
+    ``gate_out`` float32 [T, heads]."""
+    _need(q_out, "latent_prepare.q_out", dims=2)
+    _need(latent_cache, "latent_prepare.latent_cache", q_out.dtype, 4)
+    _need(q_norm_w, "latent_prepare.q_norm_w", torch.float32, 1)
+    _need(kv_norm_w, "latent_prepare.kv_norm_w", torch.float32, 1)
+    _need(block_table, "latent_prepare.block_table", torch.int32, 2)
+    T, q_rank = q_out.shape
+    kv_rank = latent_cache.shape[3]
+    n_gate = 0
+    if gate_out is not None:
+        _need(gate_out, "latent_prepare.gate_out", torch.float32, 2)
+        n_gate = gate_out.shape[1]
+    if fused.tokens != T or fused.bias is not None or latent_cache.shape[1] != 1 or latent_cache.shape[2] != page_size or \
+            q_norm_w.shape[0] != q_rank or kv_norm_w.shape[0] != kv_rank or (gate_out is not None and gate_out.shape[0] != T):
+        raise KernelError("latent_prepare: shapes differ, or a bias is pending")
+    _check(library().kestrel_latent_prepare(
+        fused.data.data_ptr(), fused.slices, fused.slice_stride, fused.width, q_norm_w.data_ptr(), kv_norm_w.data_ptr(), float(norm_eps),
+        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size), latent_cache.data_ptr(),
+        q_out.data_ptr(), _p(gate_out), _code(q_out, "latent_prepare.q_out"), T, q_rank, kv_rank, n_gate, _stream()))
+
+
+def head_gemm(x: torch.Tensor, w: torch.Tensor, heads: int, w_kn: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Every head's columns of x [T, heads * K] times that head's own matrix, a slice of ``w``:
+    ``w_kn`` False: w [heads * N, K], out_h = x_h w_h^T; True: w [heads * K, N], out_h = x_h w_h (the
+    transposed use of an expansion).  Returns [T, heads * N] in x's dtype; float32 sums."""
+    _need(x, "head_gemm.x", dims=2)
+    _need(w, "head_gemm.w", x.dtype, 2)
+    T = x.shape[0]
+    if x.shape[1] % heads or w.shape[0] % heads:
+        raise KernelError("head_gemm: the columns of x or the rows of w do not divide by the heads")
+    K = x.shape[1] // heads
+    N = w.shape[1] if w_kn else w.shape[0] // heads
+    if (w_kn and w.shape[0] != heads * K) or (not w_kn and w.shape[1] != K):
+        raise KernelError(f"head_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, {heads} heads")
+    if out is None:
+        out = torch.empty((T, heads * N), dtype=x.dtype, device=x.device)
+    _need(out, "head_gemm.out", x.dtype, 2)
+    if out.shape != (T, heads * N):
+        raise KernelError("head_gemm: out has the wrong shape")
+    _check(library().kestrel_head_gemm(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), 1 if w_kn else 0, out.data_ptr(), out.stride(0),
+                                       _code(x, "head_gemm.x"), T, heads, N, K, _stream()))
+    return out
+
+
+def head_gemm_set_plain(on: bool = True) -> None:
+    """Whether bfloat16 head-wise products take the CUDA-core kernel instead of the tensor-core one
+    (off by default).  For tests of both."""
+    library().kestrel_head_gemm_set_plain(1 if on else 0)
 
 
 # ---- gated delta rule ------------------------------------------------------------------------

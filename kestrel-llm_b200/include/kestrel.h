@@ -174,6 +174,22 @@ KESTREL_API int kestrel_attention_plain_ex(const void *q, const void *k_cache, c
 KESTREL_API int kestrel_attention_window_supported(int hd, int vd, int nq, int nkv);
 KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, kestrel_stream_t stream);
 
+/* ---- options on the scores and on the weighing of keys (attention_score.cuh); all float32 ----
+   softcap > 0: s <- softcap tanh(s / softcap); r1, r2 [nq] (both or neither): s <- s - r1[h] ln(1 + r2[h] (i - j));
+   weighting 0: softmax; 1: softmax with a valueless extra term exp(0) in the denominator; 2: every visible key weighs
+   sigmoid(s + head_bias[h]) (head_bias [nq] or NULL), not normalised over keys */
+KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, kestrel_stream_t stream);
+KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, kestrel_stream_t stream);
+/* attn_prepare_ex with a bias per product column (NULL: none); qk_norm 0: none, 1: per head (weights [hd] or NULL), 2: over the whole q and the whole k projection (weights [nq hd], [nkv hd]); v_norm: v / sqrt(mean(v^2) + eps) per head */
+KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w, const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
+
+/* ---- attention over cached latents (attention_latent.cu) ---- */
+/* product columns [q latent: q_rank | kv latent: kv_rank | gate: n_gate]: both latents RMS-normed with their weights; the query latent to q_out [T, q_rank], the kv latent into the token's slot of latent_cache [pages, 1, page_size, kv_rank], sigmoid of the gate columns to gate_out [T, n_gate] */
+KESTREL_API int kestrel_latent_prepare(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w, const float *kv_norm_w, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *latent_cache, void *q_out, float *gate_out, int dtype, int T, int q_rank, int kv_rank, int n_gate, kestrel_stream_t stream);
+/* out[t, h N + n] = sum_k x[t, h K + k] w_h[n, k]; w_kn = 0: w_h = rows [h N, (h + 1) N) of w [H N, K]; w_kn = 1: w_h[n, k] = w[h K + k, n] of w [H K, N]; all in the storage type, float32 sums */
+KESTREL_API int kestrel_head_gemm(const void *x, int ldx, const void *w, int ldw, int w_kn, void *out, int ldo, int dtype, int T, int H, int N, int K, kestrel_stream_t stream);
+KESTREL_API void kestrel_head_gemm_set_plain(int on);   /* 1: bfloat16 head-wise products take the CUDA-core kernel too; for tests of both */
+
 /* ---- gated delta rule with a decay per key channel (delta_rule.cu); state slot = [S: H d dv | tail: (taps - 1) C] float32 ---- */
 KESTREL_API int kestrel_delta_conv_silu(const float *partial, int S, long long slice_stride, int ld, const float *w, int taps, float *state, long long state_stride, long long tail_off, const int *seq_of_token, const int *cu_seqlens, const int *slots, float *out, int T, int nseq, int C, kestrel_stream_t stream);
 KESTREL_API int kestrel_delta_gates(const float *act, int C, const float *partial, int S, long long slice_stride, int ld, int col_beta, const float *a_part, int Sa, long long a_stride, const float *A_log, const float *dt_bias, float *qn, float *kn, float *decay, float *beta, int T, int H, int G, int d, kestrel_stream_t stream);

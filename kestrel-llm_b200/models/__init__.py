@@ -1,5 +1,6 @@
 from .decoder import DecoderModel, LayerCall
 from . import qwen3  # registers "Qwen3ForCausalLM"
 from . import zidivik  # registers "Zidivik"
+from . import tidavik  # registers "Tidavik"
 
-__all__ = ["DecoderModel", "LayerCall", "qwen3", "zidivik"]
+__all__ = ["DecoderModel", "LayerCall", "qwen3", "zidivik", "tidavik"]

@@ -29,12 +29,13 @@ class DecoderModel(Part):
     def __init__(self, config, dtype: torch.dtype, device, embedding: TokenEmbedding,
                  position: Optional[PositionEncoding], blocks: Sequence[Block],
                  order: Sequence[LayerCall], final_norm: Norm, lm_head: LMHead,
-                 optional_tensors: Sequence[str] = (), shared_parts: Sequence[Part] = ()):
+                 optional_tensors: Sequence[str] = (), shared_parts: Sequence[Part] = (), embedding_norm: Optional[Norm] = None):
         self.config = config
         self.dtype = dtype
         self.device = torch.device(device)
         self.embedding = embedding
         self.position = position
+        self.embedding_norm = embedding_norm                # a norm of the embedded tokens (after the position vector), or None
         self.blocks = list(blocks)
         self.order = list(order)
         self.final_norm = final_norm
@@ -66,6 +67,7 @@ class DecoderModel(Part):
         pos_ok = self.position is None or (getattr(self.position, "graph_safe", False)
                                            or type(self.position).add_to_embedding is PositionEncoding.add_to_embedding)
         return (pos_ok and all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+                and (self.embedding_norm is None or self.embedding_norm.graph_safe)
                 and self.embedding.graph_safe and self.lm_head.graph_safe)
 
     @property
@@ -80,6 +82,8 @@ class DecoderModel(Part):
         slots = self.embedding.weight_slots()
         if self.position is not None:
             slots += self.position.weight_slots()
+        if self.embedding_norm is not None:
+            slots += self.embedding_norm.weight_slots()
         for part in self.shared_parts:
             slots += part.weight_slots()
         for b in self.blocks:
@@ -92,7 +96,8 @@ class DecoderModel(Part):
         model has no ``emit`` (it then runs by the walk below).  ``cache`` is the `CacheManager`
         whose layers the program's attention operations point into."""
         from ..csrc import ops
-        pos_ok = self.position is None or type(self.position).add_to_embedding is PositionEncoding.add_to_embedding
+        pos_ok = (self.position is None or type(self.position).add_to_embedding is PositionEncoding.add_to_embedding) \
+            and self.embedding_norm is None
         blocks_ok = all(getattr(b, "emit", None) is not None and getattr(b, "emits", False) for b in self.blocks)
         if not (pos_ok and blocks_ok and all(getattr(p, "emit", None) is not None
                                               for p in (self.embedding, self.final_norm, self.lm_head))):
@@ -122,6 +127,8 @@ class DecoderModel(Part):
         x = self.embedding.forward(batch.token_ids)
         if self.position is not None:
             self.position.add_to_embedding(x, batch)
+        if self.embedding_norm is not None:                 # the stream starts as the normed embedding, still float32
+            x = self.embedding_norm.add_forward(x, None, torch.float32)
         return x, None
 
     def forward_calls(self, x, pending, batch, cache, lo: int, hi: int):

@@ -6,6 +6,7 @@ from .rotary import NoPositionEncoding, RotaryHalf, RotaryInterleaved, Sinusoida
 from .attention import GroupedQueryAttention
 from .mlp import GatedMLP
 from .attention_gated import GatedWindowAttention
+from .attention_latent import LatentAttention
 from .delta import ChannelDeltaMixer
 from .moe import RoutedExperts
 from .side_input import TokenSideInput, TokenTable
@@ -15,4 +16,4 @@ from .embedding import LMHead, TokenEmbedding
 __all__ = ["Block", "CacheSpec", "FeedForward", "FixedStateSpec", "Mixer", "Norm", "PagedKVSpec", "Part",
            "PositionEncoding", "Rotation", "WeightSlot", "Linear", "RMSNorm", "NoPositionEncoding", "RotaryHalf", "RotaryInterleaved",
            "GroupedQueryAttention", "GatedMLP", "PreNormBlock", "LMHead", "TokenEmbedding", "SinusoidalPositions",
-           "GatedWindowAttention", "ChannelDeltaMixer", "RoutedExperts", "TokenSideInput", "TokenTable", "ParallelBlock"]
+           "GatedWindowAttention", "LatentAttention", "ChannelDeltaMixer", "RoutedExperts", "TokenSideInput", "TokenTable", "ParallelBlock"]

@@ -8,6 +8,15 @@ of head n is multiplied by sigmoid(gate logit n) before the output projection.  
 norm) and V go to the request's pages; a mixer built with ``own_kv=False`` has no key and value
 projections and attends over the pages that an earlier layer of the same step wrote, with its
 own queries, mask and scale.
+
+Every one of these is a parameter, and there are more, all off by default: biases on the four
+projections (``bias``); the norm of q and k taken over the whole projection instead of per head,
+with a weight per column (``qk_norm="projection"``), or none at all (``qk_norm=None``); values of unit
+root mean square per head, cached so (``v_norm``); a cap on the scores, s <- cap * tanh(s / cap)
+(``softcap``); a distance term s <- s - r1[n] * ln(1 + r2[n] * (i - j)) with two numbers per head
+(``distance_bias``); and the way keys are weighed (``weighting``): "softmax", "softmax_sink" (the
+denominator has one more term, exp(0), that carries no value) or "sigmoid" (every visible key
+weighs sigmoid(s + pb[n]), pb a number per head if ``head_bias``; nothing is normalised over keys).
 """
 from __future__ import annotations
 
@@ -27,7 +36,9 @@ class GatedWindowAttention(Mixer):
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, v_head_dim: int, dtype: torch.dtype, device,
                  prefix: str, scale: float, norm_eps: float, window: int = 0, keep_first: int = 0, own_kv: bool = True,
                  head_gate: bool = True, cache_window: Optional[int] = None, cache_keep_first: Optional[int] = None,
-                 names=("q", "k", "v", "g", "o")):
+                 names=("q", "k", "v", "g", "o"), bias: bool = False, qk_norm: Optional[str] = "head", v_norm: bool = False,
+                 softcap: float = 0.0, distance_bias: bool = False, weighting: str = "softmax", head_bias: bool = False,
+                 extra_names=None):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
         if max(head_dim, v_head_dim) > 256:
@@ -42,8 +53,27 @@ class GatedWindowAttention(Mixer):
         self.prefix, self.names, self.dtype = prefix, names, dtype
         self.q_cols = heads * head_dim
         self.kv_cols = kv_heads * (head_dim + v_head_dim) if own_kv else 0
-        self.proj = Linear(width, self.q_cols + self.kv_cols + (heads if head_gate else 0), dtype, device)
-        self.out = Linear(heads * v_head_dim, width, dtype, device)
+        self.proj = Linear(width, self.q_cols + self.kv_cols + (heads if head_gate else 0), dtype, device, bias=bias)
+        self.out = Linear(heads * v_head_dim, width, dtype, device, bias=bias)
+        if bias and head_gate and self.proj.bias.device.type != "meta":
+            self.proj.bias[self.q_cols + self.kv_cols:].zero_()           # the gate logits have no bias
+        if qk_norm not in (None, "head", "projection"):
+            raise ValueError(f"qk_norm '{qk_norm}' is none of None, 'head', 'projection'")
+        self.qk_norm, self.v_norm = qk_norm, bool(v_norm)
+        f32 = dict(dtype=torch.float32, device=device)
+        # the norm over a whole projection has a weight per column; the norm per head has none here
+        self.q_norm_w = torch.empty((self.q_cols,), **f32) if qk_norm == "projection" else None
+        self.k_norm_w = torch.empty((kv_heads * head_dim,), **f32) if qk_norm == "projection" and own_kv else None
+        self.r1 = torch.empty((heads,), **f32) if distance_bias else None
+        self.r2 = torch.empty((heads,), **f32) if distance_bias else None
+        self.pb = torch.empty((heads,), **f32) if head_bias else None
+        if head_bias and weighting != "sigmoid":
+            raise ValueError("a number per head added to the scores changes nothing under a softmax; it belongs to sigmoid weights")
+        self.score = ops.ScoreOptions(softcap, self.r1, self.r2, self.pb, weighting)
+        self._scored = bool(softcap) or distance_bias or weighting != "softmax"
+        # checkpoint names of what the options add, after the projections' own names
+        self.extra_names = dict(bias=".b", q_norm=names[0] + ".norm", k_norm=names[1] + ".norm", r1="r1", r2="r2", head_bias="pb")
+        self.extra_names.update(extra_names or {})
 
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.kv_heads, self.head_dim, self.cache_window, self.cache_keep_first, self.v_head_dim)
@@ -58,6 +88,23 @@ class GatedWindowAttention(Mixer):
         if self.head_gate:
             slots.append(WeightSlot(p + ng, w[self.q_cols + self.kv_cols:]))
         slots.append(WeightSlot(p + no, self.out.weight))
+        x = self.extra_names
+        if self.proj.bias is not None:
+            b = self.proj.bias
+            slots.append(WeightSlot(p + nq + x["bias"], b[:self.q_cols], "bias"))
+            if self.own_kv:
+                k_end = self.q_cols + self.kv_heads * self.head_dim
+                slots += [WeightSlot(p + nk + x["bias"], b[self.q_cols:k_end], "bias"),
+                          WeightSlot(p + nv + x["bias"], b[k_end:self.q_cols + self.kv_cols], "bias")]
+            slots.append(WeightSlot(p + no + x["bias"], self.out.bias, "bias"))
+        if self.q_norm_w is not None:
+            slots.append(WeightSlot(p + x["q_norm"], self.q_norm_w, "norm"))
+        if self.k_norm_w is not None:
+            slots.append(WeightSlot(p + x["k_norm"], self.k_norm_w, "norm"))
+        if self.r1 is not None:
+            slots += [WeightSlot(p + x["r1"], self.r1, "positive"), WeightSlot(p + x["r2"], self.r2, "positive")]
+        if self.pb is not None:
+            slots.append(WeightSlot(p + x["head_bias"], self.pb, "bias"))
         return slots
 
     def forward(self, x: torch.Tensor, batch, cache) -> ops.Partials:
@@ -68,14 +115,16 @@ class GatedWindowAttention(Mixer):
         q = torch.empty((T, self.q_cols), dtype=self.dtype, device=x.device)
         gate = torch.empty((T, self.heads), dtype=torch.float32, device=x.device) if self.head_gate else None
         table = batch.block_table(cache.group)
-        ops.attn_prepare_ex(fused, None, None, True, self.norm_eps, batch.positions, batch.seq_of_token, table, cache.page_size,
-                            cache.k, cache.v, q, gate, self.heads, self.kv_heads, self.head_dim, self.v_head_dim, self.own_kv)
+        ops.attn_prepare_ex(fused, self.q_norm_w, self.k_norm_w, self.qk_norm, self.norm_eps, batch.positions, batch.seq_of_token, table,
+                            cache.page_size, cache.k, cache.v, q, gate, self.heads, self.kv_heads, self.head_dim, self.v_head_dim,
+                            self.own_kv, v_norm=self.v_norm)
+        score = self.score if self._scored else None
         a = torch.empty((T, self.heads * self.v_head_dim), dtype=self.dtype, device=x.device)
         if self.dtype == torch.bfloat16 and not self.force_plain and \
                 ops.attention_window_supported(self.head_dim, self.v_head_dim, self.heads, self.kv_heads):
             ops.attention_window(q, cache.k, cache.v, batch, table, cache.page_size, a, self.heads, self.kv_heads, self.head_dim,
-                                 self.v_head_dim, self.window, self.keep_first, gate, self.scale)
+                                 self.v_head_dim, self.window, self.keep_first, gate, self.scale, score)
         else:           # float32, and head sizes that are no multiple of 8
             ops.attention_plain_ex(q, cache.k, cache.v, batch.positions, batch.seq_of_token, table, cache.page_size, a, self.heads,
-                                   self.kv_heads, self.head_dim, self.v_head_dim, self.window, self.keep_first, gate, self.scale)
+                                   self.kv_heads, self.head_dim, self.v_head_dim, self.window, self.keep_first, gate, self.scale, score)
         return self.out.forward(a)

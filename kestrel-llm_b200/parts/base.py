@@ -26,7 +26,7 @@ class WeightSlot:
 
     ``dest`` may be a slice of a larger fused tensor (rows of a fused QKV matrix).  ``init`` is
     the distribution used by the random-weights mode: "linear" N(0, 0.02), "norm"
-    1 + N(0, 0.02), "bias" N(0, 0.02)."""
+    1 + N(0, 0.02), "bias" N(0, 0.02), "positive" |N(0, 0.02)|."""
     name: str
     dest: torch.Tensor
     init: str = "linear"
@@ -36,12 +36,15 @@ class WeightSlot:
 class PagedKVSpec:
     """Keys and values of every token, or of the last ``window`` tokens, in pages.  A windowed
     layer may keep a request's first ``keep_first`` tokens visible (their pages are then never
-    given back); values may have a size of their own."""
+    given back); values may have a size of their own.  With ``values_are_keys`` the layer caches ONE
+    vector a token and head, read both as its key and as its value (a latent that both are expanded
+    from): the V plane is the K plane."""
     kv_heads: int
     head_dim: int
     window: int = 0          # 0 = all keys
     keep_first: int = 0      # with a window: the first tokens of a request stay
     v_head_dim: int = 0      # 0 = head_dim
+    values_are_keys: bool = False
 
     @property
     def value_dim(self) -> int:

@@ -16,20 +16,20 @@ class GatedMLP(FeedForward):
     graph_safe = True
 
     def __init__(self, width: int, intermediate: int, dtype: torch.dtype, device, prefix: str,
-                 activation: str = "silu"):
+                 activation: str = "silu", names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
         if activation != "silu":
             raise ValueError(f"activation '{activation}' has no kernel; only 'silu'")
         self.width, self.intermediate = width, intermediate
-        self.prefix = prefix
+        self.prefix, self.names = prefix, names
         self.dtype = dtype
         self.gate_up = Linear(width, 2 * intermediate, dtype, device)
         self.down = Linear(intermediate, width, dtype, device)
 
     def weight_slots(self) -> List[WeightSlot]:
-        p, ff = self.prefix, self.intermediate
-        return [WeightSlot(p + "gate_proj.weight", self.gate_up.weight[:ff]),
-                WeightSlot(p + "up_proj.weight", self.gate_up.weight[ff:]),
-                WeightSlot(p + "down_proj.weight", self.down.weight)]
+        p, ff, (gate, up, down) = self.prefix, self.intermediate, self.names
+        return [WeightSlot(p + gate, self.gate_up.weight[:ff]),
+                WeightSlot(p + up, self.gate_up.weight[ff:]),
+                WeightSlot(p + down, self.down.weight)]
 
     def forward(self, x: torch.Tensor, batch, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
         act = ops.gate_up_swiglu(x, self.gate_up.weight, self.intermediate, weights_static=True)

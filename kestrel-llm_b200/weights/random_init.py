@@ -33,6 +33,8 @@ def _draw(shape, init: str, gen: torch.Generator) -> torch.Tensor:
     t.normal_(0.0, _STD, generator=gen)
     if init == "norm":
         t += 1.0
+    elif init == "positive":
+        t.abs_()
     return t
 
 
@@ -70,6 +72,8 @@ def fill_random_(model, seed: int) -> None:
                 tmp.normal_(0.0, _STD, generator=gen)
                 if slot.init == "norm":
                     tmp += 1.0
+                elif slot.init == "positive":
+                    tmp.abs_()
                 slot.dest.copy_(tmp)
             else:
                 rows = slot.dest.shape[0]
