@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
     python bench.py --workload mix14b | 32b
-    python bench.py --workload zidivik [--size a|b]
+    python bench.py --workload zidivik | tidavik [--size a|b]
 
 Default run (the headline): decode tokens a second at batch 8, at batch 1 and 64, prefill of
 2,048 tokens, and the same decode through the Python entry point with host tokens in and out.
@@ -27,6 +27,11 @@ dense decoder of equal width, heads, depth and active feed-forward size: a promp
 one step and decode steps of 8 requests at a context of 2,048, device-timed through `Engine.step`,
 plus the device time of every kind of operation in one step of each (CUDA events around each call,
 which switch the overlap of neighbours off: compare shares).
+
+`--workload tidavik`: the Tidavik decoder (window attention with sigmoid weights and a distance term,
+window attention with a softmax that has one more term, attention over cached latents; dense gated
+feed-forward) the same way, beside the Qwen3 dense decoder of equal width, heads, depth, feed-forward
+and window.
 
 Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps, with
 a synchronize on both sides.  Every step streams all weights (15 GB) and the live requests'
@@ -273,11 +278,29 @@ def zidivik_raw(z):
             "max_positions": 8192, "layers": layers}
 
 
+TIDAVIK_SIZES = {
+    # width, heads, kv heads, head sizes, window, ranks of the latent layer, feed-forward, vocab
+    "a": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, q_rank=768, kv_rank=256, ff=6144, vocab=32000),
+    "b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=2048, q_rank=1536, kv_rank=256, ff=12288, vocab=64000),
+}
+
+
+def tidavik_raw(z):
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "softcap": 50.0,
+           "mask": {"size": z["window"]}}
+    lat = {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"], "scale": z["dim"] ** -0.5,
+           "mask": {"size": z["window"]}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    layers = [{"type": "attention", "mixer": att, "mlp": mlp}, {"type": "attention_2", "mixer": att, "mlp": mlp},
+              {"type": "latent_attention", "mixer": lat, "mlp": mlp}, {"type": "attention_2", "mixer": att, "mlp": mlp}]
+    return {"architecture": "Tidavik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "max_positions": 8192, "layers": layers}
+
+
 def run_zidivik(args) -> int:
-    """Prefill and decode of the Zidivik decoder at real layer sizes, beside the Qwen3 dense decoder of equal size."""
+    """Prefill and decode of the Zidivik or the Tidavik decoder at real layer sizes, beside the Qwen3 dense decoder of equal size."""
     import numpy as np
     import torch
-    from kestrel_llm_b200.config import EngineOptions, Qwen3Config, ZidivikConfig
+    from kestrel_llm_b200.config import EngineOptions, Qwen3Config, TidavikConfig, ZidivikConfig
     from kestrel_llm_b200.config.registry import resolve_architecture
     from kestrel_llm_b200.csrc import ops
     from kestrel_llm_b200.engine import Engine, Entry
@@ -285,7 +308,8 @@ def run_zidivik(args) -> int:
 
     dev = "cuda:0"
     torch.cuda.set_device(0)
-    z = ZIDIVIK_SIZES[args.size]
+    tidavik = args.workload == "tidavik"
+    z = (TIDAVIK_SIZES if tidavik else ZIDIVIK_SIZES)[args.size]
     T, B, CTX = args.prefill_tokens, args.batch, 2048
     W, K = max(3, args.warmup), max(1, min(args.steps, 32))
     pk = peaks()
@@ -293,7 +317,7 @@ def run_zidivik(args) -> int:
     rng = np.random.default_rng(0)
     timed_names = ["linear", "add_rmsnorm", "attn_prepare", "attn_prepare_ex", "attention", "attention_plain_ex", "attention_window", "qkv_prepare_fused",
                    "gate_up_swiglu", "moe_route", "moe_experts", "delta_conv_silu", "delta_gates", "delta_scan", "delta_out", "partial_columns",
-                   "add_two", "gelu_table_mul", "add_normed", "embed", "add_sinusoid", "linear_add_into"]
+                   "add_two", "gelu_table_mul", "add_normed", "embed", "add_sinusoid", "linear_add_into", "latent_prepare", "head_gemm"]
 
     def measure(cfg, label):
         model = resolve_architecture(cfg.architecture).build(cfg, torch.bfloat16, dev)
@@ -390,15 +414,38 @@ def run_zidivik(args) -> int:
                 "decode_batch": B, "decode_context": CTX, "decode_ms": round(1000 * dec, 4), "decode_tok_s": round(B / dec, 1),
                 "launches_per_decode_step": int(launches), "device_us_per_operation": split}
 
-    raw = zidivik_raw(z)
-    zc = ZidivikConfig.from_dict(raw)
+    raw = tidavik_raw(z) if tidavik else zidivik_raw(z)
+    zc = (TidavikConfig if tidavik else ZidivikConfig).from_dict(raw)
     L = len(raw["layers"])
-    qc = Qwen3Config.from_dict(dict(QWEN3_8B, num_hidden_layers=L, hidden_size=z["width"], num_attention_heads=z["heads"],
-                                    num_key_value_heads=z["kv_heads"], head_dim=z["dim"], intermediate_size=z["top"] * z["ff"],
-                                    vocab_size=z["vocab"], max_position_embeddings=8192))
-    ours = measure(zc, "Zidivik")
-    dense = measure(qc, "Qwen3 dense, equal size")
+    dense_raw = dict(QWEN3_8B, num_hidden_layers=L, hidden_size=z["width"], num_attention_heads=z["heads"],
+                     num_key_value_heads=z["kv_heads"], head_dim=z["dim"], intermediate_size=z["ff"] if tidavik else z["top"] * z["ff"],
+                     vocab_size=z["vocab"], max_position_embeddings=8192)
+    if tidavik:                              # the dense model's layers look through the same window
+        dense_raw.update(sliding_window=z["window"], use_sliding_window=True, layer_types=["sliding_attention"] * L)
+    qc = Qwen3Config.from_dict(dense_raw)
+    ours = measure(zc, "Tidavik" if tidavik else "Zidivik")
+    dense = measure(qc, "Qwen3 dense, equal size" + (" and window" if tidavik else ""))
     clocks.close()
+    if tidavik:
+        D, H, G, d, dv, ff = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["ff"]
+        grouped_w = D * (H * d + G * (d + dv)) + H * dv * D
+        latent_w = D * (z["q_rank"] + z["kv_rank"] + H) + z["q_rank"] * H * d + H * d * z["kv_rank"] + H * dv * z["kv_rank"] + H * dv * D
+        weights = 3 * grouped_w + latent_w + L * 3 * ff * D + z["vocab"] * D
+        seen = min(T, z["window"])
+        attn = 3 * 2.0 * H * (d + dv) * T * seen + 2.0 * H * 2 * z["kv_rank"] * T * seen       # all keys of the window for every query: an upper bound
+        flops_prefill = 2.0 * T * (weights - z["vocab"] * D) + attn
+        rec = {"metric": f"Tidavik prefill tokens/s at size {args.size}, bf16, beside Qwen3 dense of equal size", "value": ours["prefill_tok_s"],
+               "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ours["prefill_ms"], "higher_is_better": True,
+               "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "ours", "workload": "tidavik",
+               "data": "synthetic: random weights, uniform random token ids, cache of the context filled with random values",
+               "config": dict(z, layers=[l["type"] for l in raw["layers"]], page_size=args.page_size, peaks=pk["source"], parallelism="single GPU"),
+               "tidavik": ours, "dense": dense,
+               "ratio_to_dense": {"prefill": round(ours["prefill_tok_s"] / dense["prefill_tok_s"], 3), "decode": round(ours["decode_tok_s"] / dense["decode_tok_s"], 3)},
+               "prefill_flops_frac_of_peak": round(flops_prefill / (ours["prefill_ms"] / 1000.0) / (pk["bf16_tflops"] * 1e12), 4),
+               "decode_weight_bytes_frac_of_hbm": round(2.0 * weights / (ours["decode_ms"] / 1000.0) / (pk["hbm_gbs"] * 1e9), 4),
+               "gpu_launches": ours["launches_per_decode_step"] * K, "clocks": clocks.summary()}
+        print(json.dumps(rec))
+        return 0
     # what a Zidivik step has to do: the weights it touches once, and its arithmetic
     D, ff, top, E = z["width"], z["ff"], z["top"], z["experts"]
     att_w = D * (z["heads"] * z["dim"] + z["kv_heads"] * (z["dim"] + z["vdim"]) + z["heads"]) + z["heads"] * z["vdim"] * D
@@ -431,10 +478,10 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps end (default 4096)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the prefill step (default 2048)")
-    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b", "zidivik"],
-                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler; zidivik: the Zidivik decoder "
+    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b", "zidivik", "tidavik"],
+                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler; zidivik / tidavik: that decoder "
                          "at real layer sizes beside Qwen3 dense of equal size")
-    ap.add_argument("--size", default="a", choices=sorted(ZIDIVIK_SIZES), help="layer sizes of --workload zidivik")
+    ap.add_argument("--size", default="a", choices=sorted(ZIDIVIK_SIZES), help="layer sizes of --workload zidivik / tidavik")
     ap.add_argument("--requests", type=int, default=0, help="requests of a workload (0: 32 for mix14b, 16 for 32b)")
     ap.add_argument("--generate", type=int, default=0, help="tokens to generate per request of a workload (0: 256 / 128)")
     ap.add_argument("--step-tokens", type=int, default=2048,
@@ -446,7 +493,7 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (no multi-GPU path exists)")
         return 2
-    if args.workload == "zidivik":
+    if args.workload in ("zidivik", "tidavik"):
         return run_zidivik(args)
     if args.workload != "decode8b":
         return run_workload(args)

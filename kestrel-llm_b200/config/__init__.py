@@ -2,8 +2,9 @@ from .model_config import ConfigError, ModelConfig, Qwen3Config, read_config_jso
 from .registry import (Architecture, architecture_of, known_architectures, load_config,
                        register_architecture, resolve_architecture)
 from .zidivik_config import ZidivikConfig
+from .tidavik_config import TidavikConfig
 from .engine_options import EngineOptions
 
-__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ZidivikConfig", "read_config_json", "Architecture",
+__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ZidivikConfig", "TidavikConfig", "read_config_json", "Architecture",
            "architecture_of", "known_architectures", "load_config", "register_architecture",
            "resolve_architecture", "EngineOptions"]

@@ -96,14 +96,19 @@ def embed(W, tokens, D, eps):
     return rms_norm(x, W["embed.norm"], eps)
 
 
-def window_mask(T: int, size: int):
-    """[T, T] booleans: row i, column j is True when 0 <= i - j < size."""
+def window_mask(T: int, size):
+    """[T, T] booleans: row i, column j is True when 0 <= i - j < size (no size: when 0 <= i - j)."""
     d = np.arange(T)[:, None] - np.arange(T)[None, :]
-    return (d >= 0) & (d < size)
+    return (d >= 0) & (d < (size if size else T))
+
+
+def mask_of(m, T):
+    return window_mask(T, (m.get("mask") or {}).get("size"))
 
 
 def soft_cap(s, cap):
-    return cap * np.tanh(s / cap)
+    """cap * tanh(s / cap); no cap (absent or 0): s."""
+    return cap * np.tanh(s / cap) if cap else s
 
 
 # ---- the three mixers ------------------------------------------------------------------------
@@ -122,12 +127,12 @@ def sigmoid_attention(W, p, m, h, eps):
     k = rms_norm(linear(h, W[p + "k"], W[p + "k.b"]), W[p + "k.norm"], eps)
     v = linear(h, W[p + "v"], W[p + "v.b"])
     q, k, v = _heads(q, H, d), _heads(k, G, d), _heads(v, G, dv)
-    vis = window_mask(T, m["mask"]["size"])
+    vis = mask_of(m, T)
     dist = np.maximum(np.arange(T)[:, None] - np.arange(T)[None, :], 0).astype(F)
     out = np.zeros((T, H, dv), dtype=F)
     for n in range(H):
         g = n // (H // G)
-        s = soft_cap((q[n] @ k[g].T) * m["scale"], m["softcap"])
+        s = soft_cap((q[n] @ k[g].T) * m["scale"], m.get("softcap"))
         s = s - W[p + "r1"][n] * np.log(1.0 + W[p + "r2"][n] * dist)
         w = np.where(vis, sigmoid(s + W[p + "pb"][n]), 0.0)
         out[:, n] = w @ v[g]
@@ -142,11 +147,11 @@ def sink_attention(W, p, m, h, eps):
     q = _heads(linear(h, W[p + "q"], W[p + "q.b"]), H, d)
     k = _heads(linear(h, W[p + "k"], W[p + "k.b"]), G, d)
     v = unit_rms(_heads(linear(h, W[p + "v"], W[p + "v.b"]), G, dv), eps)
-    vis = window_mask(T, m["mask"]["size"])
+    vis = mask_of(m, T)
     out = np.zeros((T, H, dv), dtype=F)
     for n in range(H):
         g = n // (H // G)
-        s = soft_cap((q[n] @ k[g].T) * m["scale"], m["softcap"])
+        s = soft_cap((q[n] @ k[g].T) * m["scale"], m.get("softcap"))
         e = np.where(vis, np.exp(s), 0.0)
         out[:, n] = (e / (1.0 + e.sum(axis=1, keepdims=True))) @ v[g]
     return linear(out.reshape(T, H * dv), W[p + "o"], W[p + "o.b"])
@@ -163,7 +168,7 @@ def latent_attention(W, p, m, h, eps):
     k = _heads(linear(c, W[p + "uk"]), H, d)
     v = _heads(linear(c, W[p + "uv"]), H, dv)
     gate = sigmoid(linear(h, W[p + "g"]))                             # [T, H]
-    vis = window_mask(T, m["mask"]["size"])
+    vis = mask_of(m, T)
     out = np.zeros((T, H, dv), dtype=F)
     for n in range(H):
         s = np.where(vis, (q[n] @ k[n].T) * m["scale"], -np.inf)
