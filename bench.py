@@ -317,7 +317,7 @@ def run_zidivik(args) -> int:
     rng = np.random.default_rng(0)
     timed_names = ["linear", "add_rmsnorm", "attn_prepare", "attn_prepare_ex", "attention", "attention_plain_ex", "attention_window", "qkv_prepare_fused",
                    "gate_up_swiglu", "moe_route", "moe_experts", "delta_conv_silu", "delta_gates", "delta_scan", "delta_out", "partial_columns",
-                   "add_two", "gelu_table_mul", "add_normed", "embed", "add_sinusoid", "linear_add_into", "latent_prepare", "head_gemm"]
+                   "add_two", "gelu_table_mul", "add_normed", "embed", "add_sinusoid", "linear_add_into", "latent_prepare", "head_gemm", "attention_tc"]
 
     def measure(cfg, label):
         model = resolve_architecture(cfg.architecture).build(cfg, torch.bfloat16, dev)

@@ -566,7 +566,7 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     KESTREL_REQUIRE(slices >= 1 && slice_len > 0 && slice_len % AM_BN == 0, "attention_mma: slice length %d must be a positive multiple of %d", slice_len, AM_BN);
     KESTREL_REQUIRE(slices == 1 || (part_o && part_ml), "attention_mma: %d slices without scratch", slices);
     KESTREL_REQUIRE(nkv <= 65535 && slices <= 65535, "attention_mma: grid too large");
-    AttnParams p;
+    AttnParams p = {};
     p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
     p.out = (__nv_bfloat16 *)out; p.part_o = part_o; p.part_ml = part_ml; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
     p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.block_table = block_table; p.table_stride = table_stride;

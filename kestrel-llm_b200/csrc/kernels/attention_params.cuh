@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include "common.cuh"
+#include "attention_score.cuh"
 
 struct AttnParams {
     const __nv_bfloat16 *q;         // [T, nq * hd]
@@ -19,6 +20,10 @@ struct AttnParams {
     int table_width;                // entries of a request's row that may be read (attention_tc.cu)
     int table_stride, page_size, nq, nkv, hd, window, slices, slice_len;
     float scale_log2;
+    // options on the scores and on the weighing of keys; read by attention_tc.cu only, and only if `scored`
+    float scale;
+    ScoreOpts opts;
+    int scored;
 };
 
 // Keys per slice.  A launch recorded for replay fixes the number of slices; their length then

@@ -14,12 +14,39 @@
 // One warp a head row (the blocks of a token share its head rows out), lanes over the head's
 // entries, sums of squares in float32 in a fixed shuffle tree: a token's result does not depend on
 // the batch.  For the norm over a whole projection every block first sums the squares of each q and
-// k head (a warp a head, as above) into shared memory and adds the heads' sums in ascending order.
+// k head (a warp a head, as above) into shared memory and adds the heads' sums in ascending order; the
+// columns it has summed over the product's slices stay in shared memory for the second pass where they fit.
 #include "common.cuh"
 #include <math.h>
 
 #define APX_WARPS 4
 #define APX_PER_LANE 8          // head sizes up to 256
+
+// A head's columns summed over the product's slices (ascending, from zero: the bits of `sum_slices`), plus the bias;
+// the loads of a slice's columns are all in flight at once, so a head costs one round trip a slice.
+__device__ __forceinline__ void apx_load_head(float (&x)[APX_PER_LANE], const float *__restrict__ row, int S, size_t slice_stride, int col0,
+                                              int n, int lane, const float *__restrict__ bias) {
+#pragma unroll
+    for (int c = 0; c < APX_PER_LANE; ++c) x[c] = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < S; ++s) {
+        float v[APX_PER_LANE];
+#pragma unroll
+        for (int c = 0; c < APX_PER_LANE; ++c) {
+            const int i = lane + 32 * c;
+            v[c] = i < n ? row[(size_t)s * slice_stride + col0 + i] : 0.f;
+        }
+#pragma unroll
+        for (int c = 0; c < APX_PER_LANE; ++c) x[c] += v[c];
+    }
+    if (bias) {
+#pragma unroll
+        for (int c = 0; c < APX_PER_LANE; ++c) {
+            const int i = lane + 32 * c;
+            if (i < n) x[c] += bias[col0 + i];
+        }
+    }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(APX_WARPS * 32)
@@ -28,8 +55,8 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
                        const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                        const int *__restrict__ block_table, int table_stride, int page_size,
                        T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out, float *__restrict__ gate_out,
-                       int nq, int nkv, int hd, int vd, int has_kv, const float *__restrict__ bias, int v_norm) {
-    extern __shared__ float apx_ss[];              // qk_norm = 2: sum of squares of every q and k head
+                       int nq, int nkv, int hd, int vd, int has_kv, const float *__restrict__ bias, int v_norm, int keep_x) {
+    extern __shared__ float apx_ss[];              // qk_norm = 2: sum of squares of every q and k head, then (keep_x) their columns
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -38,15 +65,16 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
     float mul_q = 1.f, mul_k = 1.f;
     if (qk_norm == 2) {
         const int n_qk = nq + (has_kv ? nkv : 0);
+        float *apx_x = apx_ss + nq + nkv;
         for (int r = warp; r < n_qk; r += APX_WARPS) {
-            float ss = 0.f;
+            float ss = 0.f, xa[APX_PER_LANE];
+            apx_load_head(xa, row, S, slice_stride, r * hd, hd, lane, bias);
 #pragma unroll
             for (int c = 0; c < APX_PER_LANE; ++c) {
                 const int i = lane + 32 * c;
                 if (i < hd) {
-                    float v = sum_slices(row, S, slice_stride, r * hd + i);
-                    if (bias) v += bias[r * hd + i];
-                    ss = fmaf(v, v, ss);
+                    if (keep_x) apx_x[r * hd + i] = xa[c];
+                    ss = fmaf(xa[c], xa[c], ss);
                 }
             }
             ss = warp_sum(ss);
@@ -73,14 +101,17 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
         const int col0 = kind == 0 ? head * hd : (kind == 1 ? nq * hd + head * hd : nq * hd + nkv * hd + head * vd);
         float x[APX_PER_LANE];
         float ss = 0.f;
+        if (keep_x && qk_norm == 2 && kind != 2) {                 // summed in the first pass
 #pragma unroll
-        for (int c = 0; c < APX_PER_LANE; ++c) {
-            const int i = lane + 32 * c;
-            float v = i < n ? sum_slices(row, S, slice_stride, col0 + i) : 0.f;
-            if (bias && i < n) v += bias[col0 + i];
-            x[c] = v;
-            ss = fmaf(v, v, ss);
+            for (int c = 0; c < APX_PER_LANE; ++c) {
+                const int i = lane + 32 * c;
+                x[c] = i < n ? apx_ss[nq + nkv + r * hd + i] : 0.f;
+            }
+        } else {
+            apx_load_head(x, row, S, slice_stride, col0, n, lane, bias);
         }
+#pragma unroll
+        for (int c = 0; c < APX_PER_LANE; ++c) ss = fmaf(x[c], x[c], ss);
         float mul = 1.f;
         const float *w = nullptr;
         if (kind != 2 && qk_norm == 1) {
@@ -121,8 +152,10 @@ KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long lo
     if (T == 0) return 0;
     KESTREL_REQUIRE(qk_norm >= 0 && qk_norm <= 2, "attn_prepare_ex: qk_norm %d is none of 0, 1, 2", qk_norm);
     KESTREL_REQUIRE(qk_norm != 2 || (q_norm_w && (k_norm_w || !has_kv)), "attn_prepare_ex: the norm over a whole projection needs its weights");
-    const size_t smem = qk_norm == 2 ? (size_t)(nq + nkv) * sizeof(float) : 0;
+    size_t smem = qk_norm == 2 ? (size_t)(nq + nkv) * sizeof(float) : 0;
     KESTREL_REQUIRE(smem <= 40000, "attn_prepare_ex: %d heads exceed the shared memory of the norm over a whole projection", nq + nkv);
+    const int keep_x = qk_norm == 2 && smem + (size_t)(nq + nkv) * hd * sizeof(float) <= 44 * 1024;
+    if (keep_x) smem += (size_t)(nq + nkv) * hd * sizeof(float);
     KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0 && vd > 0 && S > 0, "attn_prepare_ex: bad sizes");
     KESTREL_REQUIRE(hd <= 32 * APX_PER_LANE && vd <= 32 * APX_PER_LANE, "attn_prepare_ex: head size %d / %d exceeds %d", hd, vd, 32 * APX_PER_LANE);
     const int need = nq * hd + (has_kv ? nkv * (hd + vd) : 0) + (gate_out ? nq : 0);
@@ -132,11 +165,11 @@ KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long lo
     const int by = T >= 512 ? 1 : (n_heads + APX_WARPS - 1) / APX_WARPS;
     if (dtype == KESTREL_F32)
         kestrel_launch(attn_prepare_ex_kernel<float>, dim3(T, by), dim3(APX_WARPS * 32), smem, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
-                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv, bias, v_norm);
+                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv, bias, v_norm, keep_x);
     else if (dtype == KESTREL_BF16)
         kestrel_launch(attn_prepare_ex_kernel<__nv_bfloat16>, dim3(T, by), dim3(APX_WARPS * 32), smem, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, gate_out, nq, nkv,
-                       hd, vd, has_kv, bias, v_norm);
+                       hd, vd, has_kv, bias, v_norm, keep_x);
     else
         return kestrel_fail(-2, "attn_prepare_ex: unknown dtype %d", dtype);
     return kestrel_check_launch("attn_prepare_ex");

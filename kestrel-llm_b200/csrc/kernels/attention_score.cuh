@@ -38,6 +38,25 @@ struct HeadScore {
         if (dist) s -= r1 * logf(1.0f + r2 * (float)distance);
         return s + bias;
     }
+    // The same on the special-function unit, for the tensor-core kernels (their P is rounded to bfloat16
+    // anyway): tanh(x) = 1 - 2 / (1 + e^2x) from one ex2 and one rcp - an absolute error of a few 2^-23,
+    // so of cap * 1e-6 in the score, also where x is small - and the logarithm from lg2.
+    __device__ __forceinline__ float fast(float s, int distance) const {
+        if (cap > 0.f) s = fmaf(-2.0f * cap, score_rcp(1.0f + score_exp2(s * (inv_cap * 2.8853900817779268f))), cap);
+        if (dist) s -= r1 * __logf(fmaf(r2, (float)distance, 1.0f));
+        return s + bias;
+    }
+    static __device__ __forceinline__ float score_exp2(float x) {
+        float y;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+        return y;
+    }
+    static __device__ __forceinline__ float score_rcp(float x) {
+        float y;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+        return y;
+    }
 };
 
 __device__ __forceinline__ float sigmoid_f32(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_fast(float z) { return HeadScore::score_rcp(1.0f + HeadScore::score_exp2(z * -1.4426950408889634f)); }

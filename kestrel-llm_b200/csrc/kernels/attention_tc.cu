@@ -25,7 +25,10 @@
 // float32 sum no precision - and the normalisation at the end uses the same reference.
 // Keys outside [first key, last key] of a row tile are masked in S; V rows outside the CTA's
 // range are zeroed in shared memory (a page may hold another request's stale values there, and
-// 0 x NaN would not be 0).  Shared memory per CTA is 193 KB: one CTA per SM; CTAs with the most
+// 0 x NaN would not be 0).  A layer's options on the scores (`ScoreOpts`: cap, distance term, the softmax's extra
+// term, sigmoid weights) are applied by the softmax threads on the scores in their registers, on
+// the special-function unit; with sigmoid weights there is no maximum, no sum and no rescaling, P is
+// the weights.  Shared memory per CTA is 193 KB: one CTA per SM; CTAs with the most
 // keys are launched first.  Every mbarrier wait is bounded; the error word is read by
 // kestrel_attention_tc_error.  Formulas as in attention_plain.cu (reference: st.c:10779-10911,
 // st.c:9762-9859).
@@ -297,6 +300,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const uint32_t lane_base = ((uint32_t)(32 * (warp & 3))) << 16;
         const uint32_t s_addr = tmem + lane_base + x * 128, o_addr = tmem + lane_base + 256 + x * 128;
         float m_ref = -INFINITY, l_run = 0.f;       // the reference the output is accumulated against, and the row's sum
+        const bool sigmoid = p.scored && p.opts.weighting == KESTREL_WEIGH_SIGMOID, sink = p.scored && p.opts.weighting == KESTREL_WEIGH_SOFTMAX_SINK;
+        const ScoreOpts no_opts = {0.f, nullptr, nullptr, nullptr, 0};
+        const HeadScore hs(p.scored ? p.opts : no_opts, kvh * G + (row0 + x * AT_BM + (row_ok ? r : 0)) % G);
+        const float eff_scale = p.scored ? 1.f : p.scale_log2;   // transformed scores are in base-2 units already
         bool ok = true;             // after a wait gave up the loop runs on without waiting, so that the warps still meet
 
         for (int t = 0; t < n_tiles_x; ++t) {
@@ -320,6 +327,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                         if (!vis) sr[j] = 0xff800000u;
                     }
                 }
+                if (p.scored) {
+#pragma unroll
+                    for (int j = 0; j < 128; ++j) {
+                        const float raw = __uint_as_float(sr[j]);
+                        const float z = hs.fast(raw * p.scale, max(my_pos - (kbase + j), 0));
+                        const float v = sigmoid ? sigmoid_fast(z) : z * 1.4426950408889634f;
+                        sr[j] = raw == -INFINITY ? (sigmoid ? 0u : 0xff800000u) : __float_as_uint(v);
+                    }
+                }
+                if (sigmoid) {
+                    // the weights themselves are P: no maximum, no sum, nothing to rescale
+#pragma unroll
+                    for (int c = 0; c < 64; c += 16) {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(sr[2 * (c + j)]), __uint_as_float(sr[2 * (c + j) + 1]));
+                            w[j] = *reinterpret_cast<uint32_t *>(&b2);
+                        }
+                        tc_st16(s_addr + c, w);
+                    }
+                    tc_wait_st();
+                    goto p_written;
+                }
+                {
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                 for (int j = 0; j < 128; j += 8) {
@@ -327,7 +359,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                     for (int k = 0; k < 4; ++k)
                         m4[k] = at_max3(m4[k], __uint_as_float(sr[j + 2 * k]), __uint_as_float(sr[j + 2 * k + 1]));
                 }
-                const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;   // the scale is positive
+                const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * eff_scale;   // the scale is positive
                 // the reference moves only when the maximum has outgrown it by more than the step
                 const bool grow = mx > m_ref + AT_RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
                 float alpha = 1.f;
@@ -337,7 +369,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 }
                 l_run *= alpha;
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-                const uint64_t scale2 = at_pack2(p.scale_log2, p.scale_log2), shift2 = at_pack2(-m_use, -m_use);
+                const uint64_t scale2 = at_pack2(eff_scale, eff_scale), shift2 = at_pack2(-m_use, -m_use);
                 uint64_t l2[4] = {0ull, 0ull, 0ull, 0ull};          // four pairs of partial sums
                 // P over this row's own scores, which are all in registers; sixteen columns are stored
                 // while the next sixteen are computed
@@ -375,6 +407,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                     }
                 }
                 tc_wait_st();
+                }
+            p_written:;
             }
             if (kbase < k_first || kbase + AT_BN > k_hi) {
                 // V rows of keys outside the CTA's range become zero before this row tile's product
@@ -400,7 +434,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             const bool write = row_ok && ok;
             int row = row0 + x * AT_BM + r;
             size_t qrow = write ? (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G : 0;
-            const float inv = p.slices > 1 ? 1.f : 1.0f / l_run;
+            float inv = p.slices > 1 ? 1.f : 1.0f / l_run;
+            if (sigmoid) inv = 1.f;
+            if (sink) inv = 1.0f / (l_run + at_exp2(0.f - m_ref));     // one more term exp(0), against the same reference
 #pragma unroll
             for (int c = 0; c < 128; c += 32) {
                 uint32_t o[32];
@@ -468,7 +504,23 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
                                      int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd,
                                      int window, int slices, int slice_len, const int *max_kv_ptr, float scale,
                                      cudaStream_t stream) {
+    return kestrel_attention_tc_scored(q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_row0, tiles, rows_per_tile, cu_seqlens, kv_lens,
+                                       block_table, table_width, table_stride, page_size, cache_pages, T, nq, nkv, hd, window, slices, slice_len,
+                                       max_kv_ptr, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, stream);
+}
+
+// The same with a layer's options on the scores and on the weighing of keys (attention_score.cuh); with
+// options the key range is not cut into slices.
+KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, const void *v_cache, void *out,
+                                            float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
+                                            int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table,
+                                            int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd,
+                                            int window, int slices, int slice_len, const int *max_kv_ptr, float scale, float softcap,
+                                            const float *r1, const float *r2, const float *head_bias, int weighting, cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
+    const bool scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
+    KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_tc: bad score options");
+    KESTREL_REQUIRE(!scored || slices == 1, "attention_tc: options on the scores go with one slice of keys, not %d", slices);
     KESTREL_REQUIRE(hd == AT_HD, "attention_tc: head size %d; this kernel is built for %d", hd, AT_HD);
     KESTREL_REQUIRE(rows_per_tile >= 1 && rows_per_tile <= 2 * AT_BM, "attention_tc: tiles of %d rows; a CTA takes up to %d", rows_per_tile, 2 * AT_BM);
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tc: %d query heads over %d kv heads", nq, nkv);
@@ -490,6 +542,9 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
     p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window; p.slices = slices; p.slice_len = slice_len;
     p.max_kv_ptr = max_kv_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.scale = scale;
+    p.opts = {softcap, r1, r2, head_bias, weighting};
+    p.scored = scored ? 1 : 0;
     size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 1024;
     static bool attr_set = false;
     if (!attr_set) {

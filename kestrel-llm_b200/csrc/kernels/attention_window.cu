@@ -12,7 +12,10 @@
 //   KW = 1  tile of 64 rows, 16 a warp; every warp walks all key tiles (prompt portions);
 //   KW = 4  tile of 16 rows shared by the warps; key tiles of 32 go round by round, four a round,
 //           one a warp, all four computed at once; the four running (max, sum, out) states are
-//           merged in warp order at the end (decode tokens).
+//           merged in warp order at the end (decode tokens).  The rounds may be shared out over
+//           several CTAs (`ksplit`, the grid's x), each of which leaves its merged state (maximum, sum,
+//           unnormalised out) in scratch; a second kernel merges the CTAs' states in ascending order
+//           and writes the output: a step of few requests then fills the device.
 // The keys a tile can see are two ranges: the kept first tokens [0, ka) and the window
 // [kb, last position]; positions between them are never read (their pages may be gone).  Key
 // tiles go from the pages to shared memory with cp.async, the next round of tiles in flight
@@ -49,6 +52,7 @@ struct AwParams {
     float scale_log2, scale;
     ScoreOpts opts;
     int scored;                     // any of the options is on
+    float *part_o, *part_ml;        // KW = 4 with several CTAs a row tile: [seq, kv head, split, 16, D] and [.., 16, 2]
 };
 
 __device__ __forceinline__ void aw_cp_async16(uint32_t dst, const void *src, bool valid) {
@@ -62,7 +66,7 @@ attention_window_kernel(const AwParams p) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int RW = 4 / KW, BM = 16 * RW, LDS = D + 8, CH = D / 8;
-    constexpr int AW_BN = KW == 1 ? AW_BN_ROWS : (D > 128 ? AW_BN_KEYS / 2 : AW_BN_KEYS);       // head size 256: shorter tiles, the same shared memory
+    constexpr int AW_BN = KW == 1 ? (D > 128 ? AW_BN_ROWS / 2 : AW_BN_ROWS) : (D > 128 ? AW_BN_KEYS / 2 : AW_BN_KEYS);   // head size 256: shorter tiles, two CTAs an SM
     constexpr int SLOTS = 2 * KW;                     // two rounds of KW tiles
     extern __shared__ __align__(16) uint8_t aw_smem[];
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(aw_smem);      // [BM][LDS]
@@ -73,7 +77,9 @@ attention_window_kernel(const AwParams p) {
     const int kvh = blockIdx.y, seq = blockIdx.z;
     const int G = p.nq / p.nkv, hd = p.hd, vd = p.vd;
     const int tok_begin = p.cu_seqlens[seq], n_tok = p.cu_seqlens[seq + 1] - tok_begin;
-    const int n_rows = n_tok * G, row0 = blockIdx.x * BM;
+    // KW = 4: there is one row tile, and the grid's x is the CTA's share of the key rounds
+    const int split = KW == 4 ? blockIdx.x : 0, ksplit = KW == 4 ? gridDim.x : 1;
+    const int n_rows = n_tok * G, row0 = KW == 4 ? 0 : blockIdx.x * BM;
     if (row0 >= n_rows) return;
     const int rows_here = min(BM, n_rows - row0);
     const int pos_begin = p.kv_lens[seq] - n_tok;
@@ -117,7 +123,10 @@ attention_window_kernel(const AwParams p) {
         }
         aw_cp_async16((uint32_t)__cvta_generic_to_shared(Qs + r * LDS + c * 8), p.q + off, ok);
     }
-    load_round(0);                                    // Q travels with the first group
+    const int n_rounds = (n_tiles + KW - 1) / KW;
+    const int per_split = (n_rounds + ksplit - 1) / ksplit;
+    const int rd0 = split * per_split, rd1 = min(n_rounds, rd0 + per_split);
+    if (rd0 < rd1) load_round(rd0);                   // Q travels with the first group
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     // the two rows of this thread in its warp's 16-row tile: g and g + 8
@@ -143,11 +152,10 @@ attention_window_kernel(const AwParams p) {
     const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
     const int k_steps = (hd + 15) / 16, v_pairs = (vd + 15) / 16;
 
-    const int n_rounds = (n_tiles + KW - 1) / KW;
-    for (int rd = 0; rd < n_rounds; ++rd) {
+    for (int rd = rd0; rd < rd1; ++rd) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                              // round rd has landed, and everyone has left the slots that are filled next
-        if (rd + 1 < n_rounds) load_round(rd + 1);
+        if (rd + 1 < rd1) load_round(rd + 1);
         asm volatile("cp.async.commit_group;" ::: "memory");
         const int ti = rd * KW + ks, stage = (rd & 1) * KW + ks;
         if (ti < n_tiles) {
@@ -192,8 +200,8 @@ attention_window_kernel(const AwParams p) {
                     for (int c = 0; c < 4; ++c) {
                         const int s = s0 + j * 8 + 2 * tq + (c & 1), pr = pos_r[c >> 1];
                         const bool ok = s >= lo && s < up && s <= pr && (p.window <= 0 || pr - s < p.window || s < p.keep_first);
-                        const float z = ok ? hs[c >> 1](sc[j][c] * p.scale, pr - s) : 0.f;
-                        if (sigmoid) sc[j][c] = ok ? sigmoid_f32(z) : 0.f;            // the weight itself
+                        const float z = hs[c >> 1].fast(sc[j][c] * p.scale, max(pr - s, 0));
+                        if (sigmoid) sc[j][c] = ok ? sigmoid_fast(z) : 0.f;          // the weight itself
                         else sc[j][c] = ok ? z * 1.4426950408889634f : -INFINITY;
                         mx[c >> 1] = fmaxf(mx[c >> 1], sc[j][c]);
                     }
@@ -297,6 +305,30 @@ attention_window_kernel(const AwParams p) {
             }
         }
         __syncthreads();
+        if (ksplit > 1) {
+            // this CTA's share of the keys as one state: the warps' states merged in warp order, not normalised
+            const size_t base = (((size_t)seq * p.nkv + kvh) * ksplit + split) * 16;
+            for (int idx = tid; idx < rows_here * (vd + 1); idx += AW_THREADS) {
+                const int r = idx / (vd + 1), col = idx % (vd + 1);
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < KW; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
+                float L = 0.f, acc = 0.f;
+#pragma unroll
+                for (int w = 0; w < KW; ++w) {
+                    if (col == vd) {
+                        if (sm_m[w * 16 + r] != -INFINITY) L += sm_l[w * 16 + r] * fast_exp2(sm_m[w * 16 + r] - M);
+                    } else if (sigmoid) {
+                        acc += sm_o[((size_t)w * 16 + r) * D + col];
+                    } else if (sm_m[w * 16 + r] != -INFINITY) {
+                        acc += sm_o[((size_t)w * 16 + r) * D + col] * fast_exp2(sm_m[w * 16 + r] - M);
+                    }
+                }
+                if (col == vd) { p.part_ml[(base + r) * 2] = M; p.part_ml[(base + r) * 2 + 1] = L; }
+                else p.part_o[(base + r) * D + col] = acc;
+            }
+            return;
+        }
         for (int idx = tid; idx < rows_here * vd; idx += AW_THREADS) {
             const int r = idx / vd, col = idx % vd;
             float M = sink ? 0.f : -INFINITY;
@@ -319,9 +351,46 @@ attention_window_kernel(const AwParams p) {
     }
 }
 
+// KW = 4 with several CTAs a row tile: their states in ascending order of the keys, then the layer's
+// way of closing a row (the softmax's extra term, no normalisation for sigmoid weights) and the gate.
+__global__ void __launch_bounds__(AW_THREADS)
+attention_window_merge_kernel(const AwParams p, int ksplit, int D) {
+    __shared__ float f_s[64];                         // each share's factor 2^(m_s - M); then 1 / sum at [ksplit]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int kvh = blockIdx.x, seq = blockIdx.y, r = blockIdx.z, G = p.nq / p.nkv, vd = p.vd;
+    const int tok_begin = p.cu_seqlens[seq], rows_here = min(16, (p.cu_seqlens[seq + 1] - tok_begin) * G);
+    if (r >= rows_here) return;
+    const bool sigmoid = p.opts.weighting == KESTREL_WEIGH_SIGMOID, sink = p.opts.weighting == KESTREL_WEIGH_SOFTMAX_SINK;
+    const size_t base = ((size_t)seq * p.nkv + kvh) * ksplit * 16 + r;      // + s * 16
+    if (threadIdx.x < 32) {
+        // lane s holds share s (ksplit <= 32); the sum goes over the shares in ascending order
+        const int s = threadIdx.x;
+        const float m = s < ksplit ? p.part_ml[(base + (size_t)s * 16) * 2] : -INFINITY;
+        const float l = s < ksplit ? p.part_ml[(base + (size_t)s * 16) * 2 + 1] : 0.f;
+        float M = warp_max(m);
+        if (sink) M = fmaxf(M, 0.f);
+        const float f = m == -INFINITY ? 0.f : fast_exp2(m - M);
+        if (s < ksplit) f_s[s] = sigmoid ? 1.f : f;
+        float L = sink ? fast_exp2(0.f - M) : 0.f;
+        for (int k = 0; k < ksplit; ++k) L += __shfl_sync(0xffffffffu, l * f, k);
+        if (s == 0) f_s[ksplit] = sigmoid ? 1.f : 1.0f / L;
+    }
+    __syncthreads();
+    const int tok = tok_begin + r / G, head = kvh * G + r % G;
+    float inv = f_s[ksplit];
+    if (p.gate) inv *= p.gate[(size_t)tok * p.nq + head];
+    for (int col = threadIdx.x; col < vd; col += AW_THREADS) {
+        float acc = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < ksplit; ++s) acc = fmaf(p.part_o[(base + (size_t)s * 16) * D + col], f_s[s], acc);
+        p.out[((size_t)tok * p.nq + head) * vd + col] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
 template <int D, int KW>
-static int aw_launch(const AwParams &p, int nseq, int max_count, cudaStream_t stream) {
-    constexpr int BM = 16 * (4 / KW), AW_BN = KW == 1 ? AW_BN_ROWS : (D > 128 ? AW_BN_KEYS / 2 : AW_BN_KEYS);
+static int aw_launch(const AwParams &p, int nseq, int max_count, int ksplit, cudaStream_t stream) {
+    constexpr int BM = 16 * (4 / KW), AW_BN = KW == 1 ? (D > 128 ? AW_BN_ROWS / 2 : AW_BN_ROWS) : (D > 128 ? AW_BN_KEYS / 2 : AW_BN_KEYS);
     const size_t smem = (size_t)(BM + 2 * 2 * KW * AW_BN) * (D + 8) * sizeof(__nv_bfloat16);
     static bool attr_set = false;
     if (!attr_set) {
@@ -330,9 +399,32 @@ static int aw_launch(const AwParams &p, int nseq, int max_count, cudaStream_t st
         attr_set = true;
     }
     const int G = p.nq / p.nkv;
-    dim3 grid(((size_t)max_count * G + BM - 1) / BM, p.nkv, nseq);
+    dim3 grid(KW == 4 ? ksplit : ((size_t)max_count * G + BM - 1) / BM, p.nkv, nseq);
     kestrel_launch(attention_window_kernel<D, KW>, grid, dim3(AW_THREADS), smem, stream, p);
-    return kestrel_check_launch("attention_window");
+    int rc = kestrel_check_launch("attention_window");
+    if (rc || KW != 4 || ksplit == 1) return rc;
+    kestrel_launch(attention_window_merge_kernel, dim3(p.nkv, nseq, 16), dim3(AW_THREADS), 0, stream, p, ksplit, D);
+    return kestrel_check_launch("attention_window_merge");
+}
+
+// Rows of scratch (each of D + 2 floats, D = the head sizes rounded up to 32, 64, 128 or 256) a launch with `ksplit`
+// CTAs a row tile needs: 16 per request, kv head and split.
+KESTREL_API long long kestrel_attention_window_scratch_floats(int nseq, int nkv, int hd, int vd, int ksplit) {
+    const int m = hd > vd ? hd : vd, D = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
+    return (long long)nseq * nkv * ksplit * 16 * (D + 2);
+}
+
+// Into how many shares the key rounds of a step of single tokens are cut: as many as fill the device once, each of at
+// least one round; 1 for steps with portions (their row tiles fill it) and whenever the caller has no scratch.
+KESTREL_API int kestrel_attention_window_splits(int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int max_kv_len) {
+    if (nkv <= 0 || nseq <= 0 || (long long)max_count * (nq / nkv) > 16) return 1;
+    const int keys = window > 0 && window < max_kv_len ? window : max_kv_len;
+    const int tile = (hd > 128 || vd > 128) ? AW_BN_KEYS / 2 : AW_BN_KEYS;
+    const int rounds = (keys + 4 * tile - 1) / (4 * tile) + 1;
+    int k = kestrel_sms() / (nseq * nkv);
+    if (k > rounds) k = rounds;
+    if (k > 32) k = 32;
+    return k < 1 ? 1 : k;
 }
 
 // 1 if the kernel takes these sizes (the caller then need not fall back to the plain kernel)
@@ -346,15 +438,16 @@ KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, con
                                          int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
                                          cudaStream_t stream) {
     return kestrel_attention_window_scored(q, k_cache, v_cache, out, gate, cu_seqlens, kv_lens, block_table, table_stride, page_size, nseq, max_count,
-                                           nq, nkv, hd, vd, window, keep_first, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, stream);
+                                           nq, nkv, hd, vd, window, keep_first, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, 1, nullptr, stream);
 }
 
 KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate,
                                                 const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size,
                                                 int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
                                                 float softcap, const float *r1, const float *r2, const float *head_bias, int weighting,
-                                                cudaStream_t stream) {
+                                                int ksplit, float *scratch, cudaStream_t stream) {
     if (nseq == 0 || max_count == 0) return 0;
+    KESTREL_REQUIRE(ksplit >= 1 && ksplit <= 65535 && (ksplit == 1 || scratch), "attention_window: %d shares of the keys without scratch", ksplit);
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_window: bad score options");
     KESTREL_REQUIRE(kestrel_attention_window_supported(hd, vd, nq, nkv), "attention_window: head sizes %d / %d, heads %d / %d are not taken", hd, vd, nq, nkv);
     KESTREL_REQUIRE(nseq > 0 && nseq <= 65535 && nkv <= 65535 && max_count > 0 && window >= 0 && keep_first >= 0, "attention_window: bad sizes");
@@ -381,8 +474,12 @@ KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cac
     p.scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     const int D = max(hd, vd), G = nq / nkv;
     const bool keys_mode = (long long)max_count * G <= 16;
+    if (!keys_mode) ksplit = 1;
+    const int Dt = D <= 32 ? 32 : (D <= 64 ? 64 : (D <= 128 ? 128 : 256));
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + (size_t)nseq * nkv * ksplit * 16 * Dt : nullptr;
 #define AW_CASE(DD)                                                                   \
-    return keys_mode ? aw_launch<DD, 4>(p, nseq, max_count, stream) : aw_launch<DD, 1>(p, nseq, max_count, stream)
+    return keys_mode ? aw_launch<DD, 4>(p, nseq, max_count, ksplit, stream) : aw_launch<DD, 1>(p, nseq, max_count, 1, stream)
     if (D <= 32) { AW_CASE(32); }
     if (D <= 64) { AW_CASE(64); }
     if (D <= 128) { AW_CASE(128); }

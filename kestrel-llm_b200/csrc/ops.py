@@ -544,8 +544,8 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                  tile_seq: torch.Tensor, tile_row0: torch.Tensor, cu_seqlens: torch.Tensor, kv_lens: torch.Tensor,
                  block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float,
                  slices: int = 1, slice_len: int = 1 << 30, max_kv_dev: Optional[torch.Tensor] = None,
-                 rows_per_tile: int = 128) -> None:
-    """tcgen05 attention of the listed tiles, head size 128: tiles of ``rows_per_tile`` rows, up
+                 rows_per_tile: int = 128, score: Optional["ScoreOptions"] = None) -> None:
+    """tcgen05 attention of the listed tiles, head size 128 (with a layer's `ScoreOptions`, one slice): tiles of ``rows_per_tile`` rows, up
     to 256 (prompt portions; 16 for decode tokens); the key range may be cut into
     ``slices`` slices of ``slice_len`` keys (a multiple of 128) that are merged in ascending
     order; ``slices * slice_len`` must reach the longest request.  The cache tensors are
@@ -568,11 +568,11 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
         part_o = torch.empty((T * nq, slices, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((T * nq, slices, 2), dtype=torch.float32, device=q.device)
     slice_len = min(int(slice_len), (1 << 30) // 128 * 128)
-    _check(library().kestrel_attention_tc(
+    _check(library().kestrel_attention_tc_scored(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
         tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, int(rows_per_tile), cu_seqlens.data_ptr(), kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], block_table.stride(0), int(page_size), int(k_cache.shape[0]), T, nq, nkv, hd,
-        int(window), int(slices), slice_len, _p(max_kv_dev), float(scale), _stream()))
+        int(window), int(slices), slice_len, _p(max_kv_dev), float(scale), *(score or ScoreOptions()).args(nq), _stream()))
     if slices > 1:
         global launches
         launches += 1          # the merge kernel
@@ -914,10 +914,46 @@ def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         raise KernelError("attention_window: the cache planes do not fit the heads")
     if gate is not None:
         _need(gate, "attention_window.gate", torch.float32, 2)
-    _check(library().kestrel_attention_window_scored(
+    lib = library()
+    # a step of single tokens: the key range shared out over CTAs; the longest context is the host's (a recorded step's: its class's)
+    ksplit = lib.kestrel_attention_window_splits(int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, int(window), int(batch.max_kv_len)) \
+        if _window_splits else 1
+    scratch = None
+    if ksplit > 1:
+        scratch = torch.empty(lib.kestrel_attention_window_scratch_floats(int(batch.num_seqs), nkv, hd, vd, ksplit), dtype=torch.float32, device=q.device)
+    _check(lib.kestrel_attention_window_scored(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate), batch.cu_seqlens.data_ptr(), batch.kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), int(page_size), int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, int(window),
-        int(keep_first), float(scale), *(score or _NO_SCORE).args(nq), _stream()))
+        int(keep_first), float(scale), *(score or _NO_SCORE).args(nq), ksplit, _p(scratch), _stream()))
+    if ksplit > 1:
+        global launches
+        launches += 1          # the merge kernel
+
+
+_window_splits = True
+
+
+def attention_window_set_splits(on: bool = True) -> None:
+    """Whether `attention_window` shares the keys of single-token steps out over several CTAs (the default).  For tests of both."""
+    global _window_splits
+    _window_splits = bool(on)
+
+
+def row_tiles(batch, rows_per_token: int, rows_per_tile: int = 256):
+    """The step's rows - (token, head of a key head's group) pairs, ``rows_per_token`` a token - cut into tiles per
+    request: (request of each tile, its first row) as int32 tensors on the device, made once a step from the
+    host's copy of the requests' token counts and kept on ``batch``."""
+    kept = batch.__dict__.setdefault("_row_tiles", {})
+    key = (rows_per_token, rows_per_tile)
+    if key not in kept:
+        seq, row0 = [], []
+        for i, n in enumerate(batch.counts):
+            for r in range(0, n * rows_per_token, rows_per_tile):
+                seq.append(i)
+                row0.append(r)
+        t = torch.tensor([seq, row0], dtype=torch.int32).to(batch.device_buffer.device, non_blocking=True)
+        kept[key] = (t[0], t[1])
+    return kept[key]
 
 
 # ---- attention over cached latents -----------------------------------------------------------

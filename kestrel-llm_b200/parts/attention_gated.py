@@ -31,6 +31,8 @@ from .linear import Linear
 
 class GatedWindowAttention(Mixer):
     force_plain = False        # tests: bfloat16 through the plain kernel too, the twin of the tensor-core one
+    tcgen05 = True             # tests: off, portions of head size 128 stay on the mma.sync kernel
+    TC_MIN_ROWS = 64           # a step whose longest portion has more rows (tokens x heads of a group) takes the tcgen05 kernel
     graph_safe = True          # forward launches kernels over device tensors of the batch only
 
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, v_head_dim: int, dtype: torch.dtype, device,
@@ -107,7 +109,7 @@ class GatedWindowAttention(Mixer):
             slots.append(WeightSlot(p + x["head_bias"], self.pb, "bias"))
         return slots
 
-    def forward(self, x: torch.Tensor, batch, cache) -> ops.Partials:
+    def forward(self, x: torch.Tensor, batch, cache, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
         if cache.writable != self.own_kv:
             raise ValueError("a mixer with key and value projections writes its cache layer; one without reads another's")
         T = x.shape[0]
@@ -120,11 +122,19 @@ class GatedWindowAttention(Mixer):
                             self.own_kv, v_norm=self.v_norm)
         score = self.score if self._scored else None
         a = torch.empty((T, self.heads * self.v_head_dim), dtype=self.dtype, device=x.device)
-        if self.dtype == torch.bfloat16 and not self.force_plain and \
+        G = self.heads // self.kv_heads
+        if self.dtype == torch.bfloat16 and not self.force_plain and self.tcgen05 and self.head_dim == self.v_head_dim == 128 and \
+                gate is None and self.keep_first == 0 and not batch.captured and batch.max_count * G > self.TC_MIN_ROWS and \
+                ops.attention_tc_supported(128, cache.page_size):
+            # prompt portions of head size 128: the tcgen05 kernel, rows in tiles of 256 per request
+            tile_seq, tile_row0 = ops.row_tiles(batch, G, 256)
+            ops.attention_tc(q, cache.k, cache.v, a, tile_seq, tile_row0, batch.cu_seqlens, batch.kv_lens, table, cache.page_size, self.heads,
+                             self.kv_heads, 128, self.window, self.scale, rows_per_tile=256, score=score)
+        elif self.dtype == torch.bfloat16 and not self.force_plain and \
                 ops.attention_window_supported(self.head_dim, self.v_head_dim, self.heads, self.kv_heads):
             ops.attention_window(q, cache.k, cache.v, batch, table, cache.page_size, a, self.heads, self.kv_heads, self.head_dim,
                                  self.v_head_dim, self.window, self.keep_first, gate, self.scale, score)
         else:           # float32, and head sizes that are no multiple of 8
             ops.attention_plain_ex(q, cache.k, cache.v, batch.positions, batch.seq_of_token, table, cache.page_size, a, self.heads,
                                    self.kv_heads, self.head_dim, self.v_head_dim, self.window, self.keep_first, gate, self.scale, score)
-        return self.out.forward(a)
+        return self.out.forward(a, residual=residual)      # without bias and with many tokens the product adds itself to the stream

@@ -18,7 +18,7 @@ and W_g are one fused product.  The gate may be absent (``head_gate=False``).
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -62,7 +62,7 @@ class LatentAttention(Mixer):
             slots.append(WeightSlot(p + g, w[r:]))
         return slots
 
-    def forward(self, x: torch.Tensor, batch, cache) -> ops.Partials:
+    def forward(self, x: torch.Tensor, batch, cache, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
         T, H, R = x.shape[0], self.heads, self.kv_rank
         fused = self.down.forward(x)
         cq = torch.empty((T, self.q_rank), dtype=self.dtype, device=x.device)
@@ -79,4 +79,4 @@ class LatentAttention(Mixer):
             ops.attention_plain_ex(q_lat, cache.k, cache.k, batch.positions, batch.seq_of_token, table, cache.page_size, a, H, 1, R, R,
                                    self.window, 0, gate, self.scale)
         o = ops.head_gemm(a, self.up_v.weight, H, w_kn=False)                  # [T, H dv]: Uv_n (mixed latent)
-        return self.out.forward(o)
+        return self.out.forward(o, residual=residual)      # many tokens: the product adds itself to the stream

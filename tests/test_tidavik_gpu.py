@@ -211,6 +211,59 @@ def test_mixers_on_tensor_cores_against_the_plain_kernels(kind, sizes, size, pag
     assert np.abs(fast - slow).max() <= 2e-2 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("kind,sizes,size,page,n,cuts", [
+    ("attention", (8, 2, 128, 128), 300, 16, 700, [300, 400]), ("attention", (2, 2, 128, 128), 64, 32, 200, [200]),
+    ("attention", (4, 1, 128, 128), 100, 16, 300, [129, 2, 140] + [1] * 29), ("attention_2", (8, 2, 128, 128), 100, 16, 300, [129, 2, 140] + [1] * 29),
+    ("attention_2", (2, 1, 128, 128), None, 64, 400, [400]), ("attention_2", (6, 6, 128, 128), 130, 8, 520, [260, 100, 160]),
+    ("attention", (16, 1, 128, 128), 20, 16, 90, [50, 40])])
+def test_portions_of_head_size_128_on_tcgen05(kind, sizes, size, page, n, cuts):
+    """Prompt portions of head size 128 take the tcgen05 kernel with the layer's options applied to the scores in the
+    softmax threads' registers: against the plain statement and against the same mixer kept on the mma.sync kernel; several
+    key tiles, more rows than a CTA's two row tiles, windows that start inside a key tile, pages of 8 to 64."""
+    from kestrel_llm_b200.csrc import ops
+    from kestrel_llm_b200.parts import GatedWindowAttention
+    m = _m(kind, sizes, 0.3, size, 15.0)
+    calls = {"n": 0}
+    real = ops.attention_tc
+
+    def counted(*a, **kw):
+        calls["n"] += 1
+        return real(*a, **kw)
+    ops.attention_tc = counted
+    try:
+        fast, want, _ = _mixer_case(kind, "bfloat16", m, page, n, cuts, seed=5, width=64)
+    finally:
+        ops.attention_tc = real
+    ops.raise_on_kernel_error()
+    assert calls["n"] == sum(1 for c in cuts if c * (sizes[0] // sizes[1]) > GatedWindowAttention.TC_MIN_ROWS)
+    _close(fast, want, "bfloat16", f"{kind} on tcgen05")
+    GatedWindowAttention.tcgen05 = False
+    try:
+        slow, _, _ = _mixer_case(kind, "bfloat16", m, page, n, cuts, seed=5, width=64)
+    finally:
+        GatedWindowAttention.tcgen05 = True
+    assert np.abs(fast - slow).max() <= 2e-2 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("kind,sizes,size,n", [("attention", (4, 2, 64, 64), 300, 420), ("attention_2", (8, 2, 32, 48), None, 500),
+                                               ("latent_attention", (6, 16, 16, 24, 136), 260, 400), ("attention_2", (3, 3, 128, 128), 70, 200)])
+def test_single_token_steps_share_their_keys_out_over_ctas(kind, sizes, size, n):
+    """bfloat16: a step of single tokens cuts its key rounds into shares, a CTA each, merged by a second kernel - against
+    the plain statement and against the same steps with one CTA a request and key head; shares without keys included."""
+    from kestrel_llm_b200.csrc import ops
+    m = _m(kind, sizes, 0.3, size, 15.0)
+    cuts = [n - 12] + [1] * 12
+    assert ops.library().kestrel_attention_window_splits(1, 1, sizes[0], 1 if kind == "latent_attention" else sizes[1], 128, 128, size or 0, n) >= 2
+    shared, want, _ = _mixer_case(kind, "bfloat16", m, 16, n, cuts, seed=9, width=64)
+    _close(shared, want, "bfloat16", f"{kind}, keys over several CTAs")
+    ops.attention_window_set_splits(False)
+    try:
+        one, _, _ = _mixer_case(kind, "bfloat16", m, 16, n, cuts, seed=9, width=64)
+    finally:
+        ops.attention_window_set_splits(True)
+    assert np.abs(shared - one).max() <= 2e-2 * np.abs(want).max()
+
+
 @pytest.mark.parametrize("dtype,plain", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
 @pytest.mark.parametrize("T_,H,N,K", [(1, 3, 16, 24), (70, 4, 96, 64), (200, 2, 40, 136), (5, 1, 7, 5), (129, 20, 64, 16), (33, 2, 264, 72)])
 def test_head_wise_products(dtype, plain, T_, H, N, K):
@@ -321,6 +374,14 @@ def test_model_mixed_batches_pages_and_slots_used_again(tdirs, name, dtype, page
     """Up to four live requests, portions beside single tokens; nine requests through four slots and a pool that holds
     four of them, so that pages and slots are used again."""
     _run(tdirs, name, dtype, R.trace_mixed, lengths=LENGTHS_MIXED[name], page_size=page, live_max=4)
+
+
+def test_model_with_heads_of_128_mixed_batches(tdirs):
+    """bfloat16: portions of several requests in one step through the tcgen05 kernel beside single tokens on the mma.sync
+    kernel, windows longer than a key tile, pages used again."""
+    _run(tdirs, "T3", "bfloat16", R.trace_mixed, lengths=(150, 33, 400, 129, 260, 90, 16), live_max=4, sizes=(70, 2, 140, 3, 66, 2, 210, 5))
+    _run(tdirs, "T3", "bfloat16", R.trace_portions, lengths=(300, 131), sizes=(70, 2, 130, 2, 50, 3, 170, 2, 31, 4))
+    _run(tdirs, "T3", "float32", R.trace_mixed, lengths=(150, 33, 129, 90), live_max=4, sizes=(70, 2, 140, 3, 66, 2, 210, 5))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

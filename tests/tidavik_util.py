@@ -59,7 +59,14 @@ T2 = {"architecture": "Tidavik", "vocab": 97, "width": 70, "norm": {"eps": 1e-6}
     layer(sigmoid_attn(4, 4, 8, 8, 0.5, size=50, softcap=8.0), None),
     layer(latent(5, 8, 24, 16, 64, 0.45), 62),
 ]}
-CONFIGS = {"T1": (T1, 3), "T2": (T2, 8)}
+# T3: heads of 128 (prompt portions on the tcgen05 attention kernel), windows longer than a key tile of 128.
+T3 = {"architecture": "Tidavik", "vocab": 131, "width": 64, "norm": {"eps": 1e-6}, "layers": [
+    layer(sigmoid_attn(2, 1, 128, 128, 0.09, size=150, softcap=20.0), 72),
+    layer(sink_attn(4, 2, 128, 128, 0.1, size=70, softcap=25.0), None),
+    layer(latent(2, 32, 32, 48, 40, 0.2, size=200), 48),
+    layer(sink_attn(2, 2, 128, 128, 0.08, size=260), 72),
+]}
+CONFIGS = {"T1": (T1, 3), "T2": (T2, 8), "T3": (T3, 5)}
 
 
 def tensors_of(cfg: dict, seed: int) -> Dict[str, np.ndarray]:
