@@ -161,6 +161,19 @@ def test_mixer_alone_whole_and_cut(dtype, kind, sizes, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("size", [1, 2, 17])
+def test_shortest_windows_and_first_tokens(kind, dtype, size):
+    """A window of one key (the token itself), of two, and one that ends inside the second page; requests of one and two
+    tokens; the first positions, where the window is not yet full."""
+    sizes = (3, 16, 24, 40, 32) if kind == "latent_attention" else (4, 2, 16, 24)
+    m = _m(kind, sizes, 0.4, size, 6.0)
+    for n, cuts in ((1, [1]), (2, [2]), (2, [1, 1]), (40, [3, 2, 30] + [1] * 5)):
+        got, want, _ = _mixer_case(kind, dtype, m, 16, n, cuts, seed=n)
+        _close(got, want, dtype, f"{kind}, window {size}, {n} tokens as {cuts[:3]}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("where", ["window_in", "window_out", "page_border", "first_token", "far_full"])
 @pytest.mark.parametrize("kind", KINDS)
