@@ -901,7 +901,9 @@ def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      out: torch.Tensor, nq: int, nkv: int, hd: int, vd: int, window: int, keep_first: int, gate: Optional[torch.Tensor],
                      scale: float, score: Optional[ScoreOptions] = None) -> None:
     """`attention_plain_ex` for bfloat16 on the tensor cores, over this step's requests as ``batch``
-    describes them (cumulative lengths, lengths after the step and the most tokens of one request)."""
+    describes them (cumulative lengths, lengths after the step, the most tokens of one request and the
+    longest context).  A step of single tokens cuts its key rounds into shares, a CTA each, and a
+    second kernel merges them (`attention_window_set_splits`)."""
     _need(q, "attention_window.q", torch.bfloat16, 2)
     _need(out, "attention_window.out", torch.bfloat16, 2)
     _need(k_cache, "attention_window.k_cache", torch.bfloat16, 4)

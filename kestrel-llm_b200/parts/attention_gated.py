@@ -17,6 +17,11 @@ root mean square per head, cached so (``v_norm``); a cap on the scores, s <- cap
 (``distance_bias``); and the way keys are weighed (``weighting``): "softmax", "softmax_sink" (the
 denominator has one more term, exp(0), that carries no value) or "sigmoid" (every visible key
 weighs sigmoid(s + pb[n]), pb a number per head if ``head_bias``; nothing is normalised over keys).
+
+Kernels: float32 and head sizes that are no multiples of 8 run on the plain kernel; bfloat16 on the
+``mma.sync`` kernel of `ops.attention_window` (single-token steps share their keys out over CTAs),
+except steps with prompt portions of head size 128 without gate and kept tokens, which take the
+tcgen05 kernel (`ops.attention_tc`) with the same options.
 """
 from __future__ import annotations
 
