@@ -15,7 +15,8 @@
 //           merged in warp order at the end (decode tokens).  The rounds may be shared out over
 //           several CTAs (`ksplit`, the grid's x), each of which leaves its merged state (maximum, sum,
 //           unnormalised out) in scratch; a second kernel merges the CTAs' states in ascending order
-//           and writes the output: a step of few requests then fills the device.
+//           and writes the output: a step of few requests then fills the device.  Requests of up to 64
+//           rows (two tokens of 32 heads on one key head, say) go this way as row tiles of 16.
 // The keys a tile can see are two ranges: the kept first tokens [0, ka) and the window
 // [kb, last position]; positions between them are never read (their pages may be gone).  Key
 // tiles go from the pages to shared memory with cp.async, the next round of tiles in flight
@@ -52,7 +53,8 @@ struct AwParams {
     float scale_log2, scale;
     ScoreOpts opts;
     int scored;                     // any of the options is on
-    float *part_o, *part_ml;        // KW = 4 with several CTAs a row tile: [seq, kv head, split, 16, D] and [.., 16, 2]
+    float *part_o, *part_ml;        // KW = 4 with several CTAs a row tile: [seq, kv head, row tile, split, 16, D] and [.., 16, 2]
+    int ksplit, row_tiles;          // KW = 4: shares of the key rounds a row tile, and row tiles of 16 a request (the grid's x is their product)
 };
 
 __device__ __forceinline__ void aw_cp_async16(uint32_t dst, const void *src, bool valid) {
@@ -77,9 +79,10 @@ attention_window_kernel(const AwParams p) {
     const int kvh = blockIdx.y, seq = blockIdx.z;
     const int G = p.nq / p.nkv, hd = p.hd, vd = p.vd;
     const int tok_begin = p.cu_seqlens[seq], n_tok = p.cu_seqlens[seq + 1] - tok_begin;
-    // KW = 4: there is one row tile, and the grid's x is the CTA's share of the key rounds
-    const int split = KW == 4 ? blockIdx.x : 0, ksplit = KW == 4 ? gridDim.x : 1;
-    const int n_rows = n_tok * G, row0 = KW == 4 ? 0 : blockIdx.x * BM;
+    // KW = 4: the grid's x counts (row tile, share of the key rounds) pairs
+    const int ksplit = KW == 4 ? p.ksplit : 1, split = KW == 4 ? blockIdx.x % ksplit : 0;
+    const int rt_idx = KW == 4 ? blockIdx.x / ksplit : blockIdx.x;
+    const int n_rows = n_tok * G, row0 = rt_idx * BM;
     if (row0 >= n_rows) return;
     const int rows_here = min(BM, n_rows - row0);
     const int pos_begin = p.kv_lens[seq] - n_tok;
@@ -307,7 +310,7 @@ attention_window_kernel(const AwParams p) {
         __syncthreads();
         if (ksplit > 1) {
             // this CTA's share of the keys as one state: the warps' states merged in warp order, not normalised
-            const size_t base = (((size_t)seq * p.nkv + kvh) * ksplit + split) * 16;
+            const size_t base = ((((size_t)seq * p.nkv + kvh) * p.row_tiles + rt_idx) * ksplit + split) * 16;
             for (int idx = tid; idx < rows_here * (vd + 1); idx += AW_THREADS) {
                 const int r = idx / (vd + 1), col = idx % (vd + 1);
                 float M = -INFINITY;
@@ -358,11 +361,12 @@ attention_window_merge_kernel(const AwParams p, int ksplit, int D) {
     __shared__ float f_s[64];                         // each share's factor 2^(m_s - M); then 1 / sum at [ksplit]
     pdl_launch_dependents();
     pdl_wait();
-    const int kvh = blockIdx.x, seq = blockIdx.y, r = blockIdx.z, G = p.nq / p.nkv, vd = p.vd;
-    const int tok_begin = p.cu_seqlens[seq], rows_here = min(16, (p.cu_seqlens[seq + 1] - tok_begin) * G);
-    if (r >= rows_here) return;
+    const int kvh = blockIdx.x, seq = blockIdx.y, row = blockIdx.z, G = p.nq / p.nkv, vd = p.vd;   // row among the request's rows
+    const int tok_begin = p.cu_seqlens[seq];
+    if (row >= (p.cu_seqlens[seq + 1] - tok_begin) * G) return;
+    const int r = row % 16;
     const bool sigmoid = p.opts.weighting == KESTREL_WEIGH_SIGMOID, sink = p.opts.weighting == KESTREL_WEIGH_SOFTMAX_SINK;
-    const size_t base = ((size_t)seq * p.nkv + kvh) * ksplit * 16 + r;      // + s * 16
+    const size_t base = (((size_t)seq * p.nkv + kvh) * p.row_tiles + row / 16) * ksplit * 16 + r;      // + s * 16
     if (threadIdx.x < 32) {
         // lane s holds share s (ksplit <= 32); the sum goes over the shares in ascending order
         const int s = threadIdx.x;
@@ -377,7 +381,7 @@ attention_window_merge_kernel(const AwParams p, int ksplit, int D) {
         if (s == 0) f_s[ksplit] = sigmoid ? 1.f : 1.0f / L;
     }
     __syncthreads();
-    const int tok = tok_begin + r / G, head = kvh * G + r % G;
+    const int tok = tok_begin + row / G, head = kvh * G + row % G;
     float inv = f_s[ksplit];
     if (p.gate) inv *= p.gate[(size_t)tok * p.nq + head];
     for (int col = threadIdx.x; col < vd; col += AW_THREADS) {
@@ -399,29 +403,33 @@ static int aw_launch(const AwParams &p, int nseq, int max_count, int ksplit, cud
         attr_set = true;
     }
     const int G = p.nq / p.nkv;
-    dim3 grid(KW == 4 ? ksplit : ((size_t)max_count * G + BM - 1) / BM, p.nkv, nseq);
+    dim3 grid(KW == 4 ? ksplit * p.row_tiles : ((size_t)max_count * G + BM - 1) / BM, p.nkv, nseq);
     kestrel_launch(attention_window_kernel<D, KW>, grid, dim3(AW_THREADS), smem, stream, p);
     int rc = kestrel_check_launch("attention_window");
     if (rc || KW != 4 || ksplit == 1) return rc;
-    kestrel_launch(attention_window_merge_kernel, dim3(p.nkv, nseq, 16), dim3(AW_THREADS), 0, stream, p, ksplit, D);
+    kestrel_launch(attention_window_merge_kernel, dim3(p.nkv, nseq, 16 * p.row_tiles), dim3(AW_THREADS), 0, stream, p, ksplit, D);
     return kestrel_check_launch("attention_window_merge");
 }
 
-// Rows of scratch (each of D + 2 floats, D = the head sizes rounded up to 32, 64, 128 or 256) a launch with `ksplit`
-// CTAs a row tile needs: 16 per request, kv head and split.
-KESTREL_API long long kestrel_attention_window_scratch_floats(int nseq, int nkv, int hd, int vd, int ksplit) {
+#define AW_KEYS_MODE_ROWS 64     // steps whose requests bring at most this many rows (tokens x heads of a group) walk the keys in rounds
+
+// Floats of scratch a launch with `ksplit` CTAs a row tile needs: 16 rows of D + 2 (D = the head sizes rounded up to
+// 32, 64, 128 or 256) per request, kv head, row tile and share.
+KESTREL_API long long kestrel_attention_window_scratch_floats(int nseq, int max_count, int nq, int nkv, int hd, int vd, int ksplit) {
     const int m = hd > vd ? hd : vd, D = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
-    return (long long)nseq * nkv * ksplit * 16 * (D + 2);
+    const long long row_tiles = ((long long)max_count * (nq / nkv) + 15) / 16;
+    return (long long)nseq * nkv * row_tiles * ksplit * 16 * (D + 2);
 }
 
 // Into how many shares the key rounds of a step of single tokens are cut: as many as fill the device once, each of at
 // least one round; 1 for steps with portions (their row tiles fill it) and whenever the caller has no scratch.
 KESTREL_API int kestrel_attention_window_splits(int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int max_kv_len) {
-    if (nkv <= 0 || nseq <= 0 || (long long)max_count * (nq / nkv) > 16) return 1;
+    if (nkv <= 0 || nseq <= 0 || (long long)max_count * (nq / nkv) > AW_KEYS_MODE_ROWS) return 1;
+    const int row_tiles = (max_count * (nq / nkv) + 15) / 16;
     const int keys = window > 0 && window < max_kv_len ? window : max_kv_len;
     const int tile = (hd > 128 || vd > 128) ? AW_BN_KEYS / 2 : AW_BN_KEYS;
     const int rounds = (keys + 4 * tile - 1) / (4 * tile) + 1;
-    int k = kestrel_sms() / (nseq * nkv);
+    int k = kestrel_sms() / (nseq * nkv * row_tiles);
     if (k > rounds) k = rounds;
     if (k > 32) k = 32;
     return k < 1 ? 1 : k;
@@ -473,11 +481,13 @@ KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cac
     p.opts = {softcap, r1, r2, head_bias, weighting};
     p.scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     const int D = max(hd, vd), G = nq / nkv;
-    const bool keys_mode = (long long)max_count * G <= 16;
+    const bool keys_mode = (long long)max_count * G <= AW_KEYS_MODE_ROWS;
     if (!keys_mode) ksplit = 1;
     const int Dt = D <= 32 ? 32 : (D <= 64 ? 64 : (D <= 128 ? 128 : 256));
+    p.ksplit = ksplit;
+    p.row_tiles = keys_mode ? (max_count * G + 15) / 16 : 1;
     p.part_o = scratch;
-    p.part_ml = scratch ? scratch + (size_t)nseq * nkv * ksplit * 16 * Dt : nullptr;
+    p.part_ml = scratch ? scratch + (size_t)nseq * nkv * p.row_tiles * ksplit * 16 * Dt : nullptr;
 #define AW_CASE(DD)                                                                   \
     return keys_mode ? aw_launch<DD, 4>(p, nseq, max_count, ksplit, stream) : aw_launch<DD, 1>(p, nseq, max_count, 1, stream)
     if (D <= 32) { AW_CASE(32); }

@@ -922,7 +922,7 @@ def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         if _window_splits else 1
     scratch = None
     if ksplit > 1:
-        scratch = torch.empty(lib.kestrel_attention_window_scratch_floats(int(batch.num_seqs), nkv, hd, vd, ksplit), dtype=torch.float32, device=q.device)
+        scratch = torch.empty(lib.kestrel_attention_window_scratch_floats(int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, ksplit), dtype=torch.float32, device=q.device)
     _check(lib.kestrel_attention_window_scored(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate), batch.cu_seqlens.data_ptr(), batch.kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), int(page_size), int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, int(window),

@@ -259,13 +259,15 @@ def test_portions_of_head_size_128_on_tcgen05(kind, sizes, size, page, n, cuts):
 
 
 @pytest.mark.parametrize("kind,sizes,size,n", [("attention", (4, 2, 64, 64), 300, 420), ("attention_2", (8, 2, 32, 48), None, 500),
-                                               ("latent_attention", (6, 16, 16, 24, 136), 260, 400), ("attention_2", (3, 3, 128, 128), 70, 200)])
+                                               ("latent_attention", (6, 16, 16, 24, 136), 260, 400), ("attention_2", (3, 3, 128, 128), 70, 200),
+                                               ("latent_attention", (20, 16, 16, 24, 64), 200, 330), ("attention", (24, 1, 32, 32), 100, 300)])
 def test_single_token_steps_share_their_keys_out_over_ctas(kind, sizes, size, n):
     """bfloat16: a step of single tokens cuts its key rounds into shares, a CTA each, merged by a second kernel - against
-    the plain statement and against the same steps with one CTA a request and key head; shares without keys included."""
+    the plain statement and against the same steps with one CTA a request and key head; shares without keys, requests
+    of several row tiles of 16 (twenty heads on one key head, a portion of two tokens) included."""
     from kestrel_llm_b200.csrc import ops
     m = _m(kind, sizes, 0.3, size, 15.0)
-    cuts = [n - 12] + [1] * 12
+    cuts = [n - 12, 2] + [1] * 10
     assert ops.library().kestrel_attention_window_splits(1, 1, sizes[0], 1 if kind == "latent_attention" else sizes[1], 128, 128, size or 0, n) >= 2
     shared, want, _ = _mixer_case(kind, "bfloat16", m, 16, n, cuts, seed=9, width=64)
     _close(shared, want, "bfloat16", f"{kind}, keys over several CTAs")
