@@ -47,7 +47,7 @@ T1 = {"architecture": "Tidavik", "vocab": 173, "width": 72, "norm": {"eps": 1e-5
     layer(sigmoid_attn(4, 2, 16, 24, 0.3, size=24, softcap=30.0), None),
     layer(sink_attn(6, 2, 8, 40, 0.5, size=9, softcap=12.0), 40),
     layer(sigmoid_attn(2, 2, 32, 8, 0.25, size=40, softcap=5.0), 56),
-    layer(latent(1, 16, 48, 24, 56, 0.3, size=33), None),
+    layer(latent(1, 16, 48, 24, 56, 0.3, size=24), None),              # the window of layer 1: one cache group, planes of two shapes
     layer(sink_attn(2, 1, 24, 16, 0.2, size=70, softcap=40.0), 88),
 ]}
 # T2: a width and head sizes that are no multiples of 8 (the plain kernels in bfloat16 too); a layer that sees every earlier
