@@ -46,6 +46,21 @@ struct HeadScore {
         if (dist) s -= r1 * __logf(fmaf(r2, (float)distance, 1.0f));
         return s + bias;
     }
+    // The same with the layer's options as compile-time facts, for loops over many scores: nothing of an option that
+    // is off is issued.  Returns the score in base-2 units (times log2 e) unless SIGMOID, which returns the weight.
+    template <bool CAP, bool DIST, bool SIGMOID>
+    __device__ __forceinline__ float fast_as(float s, int distance) const {
+        constexpr float LOG2E = 1.4426950408889634f;
+        if (SIGMOID) {
+            if (CAP) s = fmaf(-2.0f * cap, score_rcp(1.0f + score_exp2(s * (inv_cap * 2.8853900817779268f))), cap);
+            if (DIST) s -= r1 * __logf(fmaf(r2, (float)distance, 1.0f));
+            return score_rcp(1.0f + score_exp2((s + bias) * -LOG2E));
+        }
+        if (CAP) s = fmaf(-2.0f * LOG2E * cap, score_rcp(1.0f + score_exp2(s * (inv_cap * 2.8853900817779268f))), LOG2E * cap);
+        else s *= LOG2E;
+        if (DIST) s -= (LOG2E * r1) * __logf(fmaf(r2, (float)distance, 1.0f));
+        return s;
+    }
     static __device__ __forceinline__ float score_exp2(float x) {
         float y;
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

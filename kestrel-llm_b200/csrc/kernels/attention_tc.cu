@@ -317,23 +317,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
                 for (int c = 0; c < 128; c += 32) at_ld32(s_addr + c, sr + c);
                 at_ld_wait();
+                if (p.scored) {
+                    // the layer's options on the raw scores, before the mask (a key that may not be seen is overwritten
+                    // below, whatever its transformed score); the two layer kinds in use as loops of their own
+                    const int d0 = my_pos - kbase;
+                    if (hs.cap > 0.f && !hs.dist && !sigmoid) {
+#pragma unroll
+                        for (int j = 0; j < 128; ++j) sr[j] = __float_as_uint(hs.fast_as<true, false, false>(__uint_as_float(sr[j]) * p.scale, 0));
+                    } else if (hs.cap > 0.f && hs.dist && sigmoid) {
+#pragma unroll
+                        for (int j = 0; j < 128; ++j) sr[j] = __float_as_uint(hs.fast_as<true, true, true>(__uint_as_float(sr[j]) * p.scale, max(d0 - j, 0)));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 128; ++j) {
+                            const float z = hs.fast(__uint_as_float(sr[j]) * p.scale, max(d0 - j, 0));
+                            sr[j] = __float_as_uint(sigmoid ? sigmoid_fast(z) : z * 1.4426950408889634f);
+                        }
+                    }
+                }
                 const bool whole = kbase >= k_first && kbase + AT_BN <= k_hi_x && kbase + AT_BN - 1 <= my_pos && kbase >= my_lo;
                 if (!__all_sync(0xffffffffu, whole)) {
-                    // keys this row may not see count as minus infinity: no maximum, a weight of zero
+                    // keys this row may not see count as minus infinity: no maximum, a weight of zero (sigmoid weights: zero itself)
+                    const uint32_t hidden = sigmoid ? 0u : 0xff800000u;
 #pragma unroll
                     for (int j = 0; j < 128; ++j) {
                         int key = kbase + j;
                         bool vis = key <= my_pos && key >= my_lo && key < k_hi_x && key >= k_first;
-                        if (!vis) sr[j] = 0xff800000u;
-                    }
-                }
-                if (p.scored) {
-#pragma unroll
-                    for (int j = 0; j < 128; ++j) {
-                        const float raw = __uint_as_float(sr[j]);
-                        const float z = hs.fast(raw * p.scale, max(my_pos - (kbase + j), 0));
-                        const float v = sigmoid ? sigmoid_fast(z) : z * 1.4426950408889634f;
-                        sr[j] = raw == -INFINITY ? (sigmoid ? 0u : 0xff800000u) : __float_as_uint(v);
+                        if (!vis) sr[j] = hidden;
                     }
                 }
                 if (sigmoid) {
