@@ -25,9 +25,11 @@
 #include "mma_sync.cuh"
 #include <math.h>
 
-#define LP_THREADS 128
+#define LP_THREADS 128          // threads a token of steps with many tokens; few tokens take LP_THREADS_FEW
+#define LP_THREADS_FEW 512
 
 // sum over the block in a fixed order: lanes by the shuffle tree, warps in ascending order
+template <int THREADS>
 __device__ __forceinline__ float lp_block_sum(float v, float *scratch) {
     v = warp_sum(v);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -36,39 +38,41 @@ __device__ __forceinline__ float lp_block_sum(float v, float *scratch) {
     __syncthreads();
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < LP_THREADS / 32; ++w) t += scratch[w];
+    for (int w = 0; w < THREADS / 32; ++w) t += scratch[w];
     return t;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(LP_THREADS)
+// The order of a sum of squares depends on THREADS.  float32 always runs LP_THREADS (a token's bits do not depend on
+// the step it is in); bfloat16 steps of few tokens take more threads a token, and differ by the rounding of that sum.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 latent_prepare_kernel(const float *__restrict__ partial, int S, size_t slice_stride, int ld, const float *__restrict__ q_w,
                       const float *__restrict__ kv_w, float eps, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                       const int *__restrict__ block_table, int table_stride, int page_size, T *__restrict__ latent_cache,
                       T *__restrict__ q_out, float *__restrict__ gate_out, int q_rank, int kv_rank, int n_gate) {
-    __shared__ float scratch[LP_THREADS / 32];
+    __shared__ float scratch[THREADS / 32];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, tid = threadIdx.x;
     const float *row = partial + (size_t)t * ld;
     float sq = 0.f, sk = 0.f;
-    for (int i = tid; i < q_rank; i += LP_THREADS) {
+    for (int i = tid; i < q_rank; i += THREADS) {
         const float v = sum_slices(row, S, slice_stride, i);
         sq = fmaf(v, v, sq);
     }
-    for (int i = tid; i < kv_rank; i += LP_THREADS) {
+    for (int i = tid; i < kv_rank; i += THREADS) {
         const float v = sum_slices(row, S, slice_stride, q_rank + i);
         sk = fmaf(v, v, sk);
     }
-    const float mul_q = 1.0f / sqrtf(lp_block_sum(sq, scratch) / (float)q_rank + eps);
-    const float mul_k = 1.0f / sqrtf(lp_block_sum(sk, scratch) / (float)kv_rank + eps);
+    const float mul_q = 1.0f / sqrtf(lp_block_sum<THREADS>(sq, scratch) / (float)q_rank + eps);
+    const float mul_k = 1.0f / sqrtf(lp_block_sum<THREADS>(sk, scratch) / (float)kv_rank + eps);
     T *qrow = q_out + (size_t)t * q_rank;
-    for (int i = tid; i < q_rank; i += LP_THREADS) qrow[i] = from_f32<T>(sum_slices(row, S, slice_stride, i) * mul_q * q_w[i]);
+    for (int i = tid; i < q_rank; i += THREADS) qrow[i] = from_f32<T>(sum_slices(row, S, slice_stride, i) * mul_q * q_w[i]);
     const int pos = positions[t];
     const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
     T *crow = latent_cache + ((size_t)page * page_size + (pos % page_size)) * kv_rank;
-    for (int i = tid; i < kv_rank; i += LP_THREADS) crow[i] = from_f32<T>(sum_slices(row, S, slice_stride, q_rank + i) * mul_k * kv_w[i]);
-    for (int h = tid; h < n_gate; h += LP_THREADS)
+    for (int i = tid; i < kv_rank; i += THREADS) crow[i] = from_f32<T>(sum_slices(row, S, slice_stride, q_rank + i) * mul_k * kv_w[i]);
+    for (int h = tid; h < n_gate; h += THREADS)
         gate_out[(size_t)t * n_gate + h] = 1.0f / (1.0f + expf(-sum_slices(row, S, slice_stride, q_rank + kv_rank + h)));
 }
 
@@ -80,10 +84,14 @@ KESTREL_API int kestrel_latent_prepare(const float *partial, int S, long long sl
     KESTREL_REQUIRE(T > 0 && S > 0 && q_rank > 0 && kv_rank > 0 && n_gate >= 0 && (n_gate == 0 || gate_out), "latent_prepare: bad sizes");
     KESTREL_REQUIRE(ld >= q_rank + kv_rank + n_gate, "latent_prepare: the product has %d columns, the latents and gates need %d", ld, q_rank + kv_rank + n_gate);
     if (dtype == KESTREL_F32)
-        kestrel_launch(latent_prepare_kernel<float>, dim3(T), dim3(LP_THREADS), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, kv_norm_w, norm_eps,
+        kestrel_launch(latent_prepare_kernel<float, LP_THREADS>, dim3(T), dim3(LP_THREADS), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, kv_norm_w, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (float *)latent_cache, (float *)q_out, gate_out, q_rank, kv_rank, n_gate);
+    else if (dtype == KESTREL_BF16 && T <= 64)
+        kestrel_launch(latent_prepare_kernel<__nv_bfloat16, LP_THREADS_FEW>, dim3(T), dim3(LP_THREADS_FEW), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, kv_norm_w, norm_eps,
+                       positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)latent_cache, (__nv_bfloat16 *)q_out, gate_out, q_rank, kv_rank,
+                       n_gate);
     else if (dtype == KESTREL_BF16)
-        kestrel_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(LP_THREADS), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, kv_norm_w, norm_eps,
+        kestrel_launch(latent_prepare_kernel<__nv_bfloat16, LP_THREADS>, dim3(T), dim3(LP_THREADS), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, kv_norm_w, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)latent_cache, (__nv_bfloat16 *)q_out, gate_out, q_rank, kv_rank,
                        n_gate);
     else
