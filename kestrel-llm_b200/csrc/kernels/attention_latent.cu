@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(THREADS)
 latent_prepare_kernel(const float *__restrict__ partial, int S, size_t slice_stride, int ld, const float *__restrict__ q_w,
                       const float *__restrict__ kv_w, float eps, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                       const int *__restrict__ block_table, int table_stride, int page_size, T *__restrict__ latent_cache,
-                      T *__restrict__ q_out, float *__restrict__ gate_out, int q_rank, int kv_rank, int n_gate) {
+                      T *__restrict__ q_out, float *__restrict__ gate_out, int q_rank, int kv_rank, int n_gate, T *__restrict__ kv_out) {
     __shared__ float scratch[THREADS / 32];
     pdl_launch_dependents();
     pdl_wait();
@@ -71,32 +71,58 @@ latent_prepare_kernel(const float *__restrict__ partial, int S, size_t slice_str
     const int pos = positions[t];
     const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
     T *crow = latent_cache + ((size_t)page * page_size + (pos % page_size)) * kv_rank;
-    for (int i = tid; i < kv_rank; i += THREADS) crow[i] = from_f32<T>(sum_slices(row, S, slice_stride, q_rank + i) * mul_k * kv_w[i]);
+    T *orow = kv_out ? kv_out + (size_t)t * kv_rank : nullptr;      // the step's latents as rows too, for callers that expand them
+    for (int i = tid; i < kv_rank; i += THREADS) {
+        const T c = from_f32<T>(sum_slices(row, S, slice_stride, q_rank + i) * mul_k * kv_w[i]);
+        crow[i] = c;
+        if (orow) orow[i] = c;
+    }
     for (int h = tid; h < n_gate; h += THREADS)
         gate_out[(size_t)t * n_gate + h] = 1.0f / (1.0f + expf(-sum_slices(row, S, slice_stride, q_rank + kv_rank + h)));
 }
 
 KESTREL_API int kestrel_latent_prepare(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w, const float *kv_norm_w,
                                        float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride,
-                                       int page_size, void *latent_cache, void *q_out, float *gate_out, int dtype, int T, int q_rank, int kv_rank,
-                                       int n_gate, cudaStream_t stream) {
+                                       int page_size, void *latent_cache, void *q_out, float *gate_out, void *kv_out, int dtype, int T, int q_rank,
+                                       int kv_rank, int n_gate, cudaStream_t stream) {
     if (T == 0) return 0;
     KESTREL_REQUIRE(T > 0 && S > 0 && q_rank > 0 && kv_rank > 0 && n_gate >= 0 && (n_gate == 0 || gate_out), "latent_prepare: bad sizes");
     KESTREL_REQUIRE(ld >= q_rank + kv_rank + n_gate, "latent_prepare: the product has %d columns, the latents and gates need %d", ld, q_rank + kv_rank + n_gate);
     if (dtype == KESTREL_F32)
         kestrel_launch(latent_prepare_kernel<float, LP_THREADS>, dim3(T), dim3(LP_THREADS), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, kv_norm_w, norm_eps,
-                       positions, seq_of_token, block_table, table_stride, page_size, (float *)latent_cache, (float *)q_out, gate_out, q_rank, kv_rank, n_gate);
+                       positions, seq_of_token, block_table, table_stride, page_size, (float *)latent_cache, (float *)q_out, gate_out, q_rank, kv_rank, n_gate, (float *)kv_out);
     else if (dtype == KESTREL_BF16 && T <= 64)
         kestrel_launch(latent_prepare_kernel<__nv_bfloat16, LP_THREADS_FEW>, dim3(T), dim3(LP_THREADS_FEW), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, kv_norm_w, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)latent_cache, (__nv_bfloat16 *)q_out, gate_out, q_rank, kv_rank,
-                       n_gate);
+                       n_gate, (__nv_bfloat16 *)kv_out);
     else if (dtype == KESTREL_BF16)
         kestrel_launch(latent_prepare_kernel<__nv_bfloat16, LP_THREADS>, dim3(T), dim3(LP_THREADS), 0, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, kv_norm_w, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)latent_cache, (__nv_bfloat16 *)q_out, gate_out, q_rank, kv_rank,
-                       n_gate);
+                       n_gate, (__nv_bfloat16 *)kv_out);
     else
         return kestrel_fail(-2, "latent_prepare: unknown dtype %d", dtype);
     return kestrel_check_launch("latent_prepare");
+}
+
+// x[t, h, :] *= gate[t, h]: a gate per head on rows of heads, in place
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_scale_kernel(T *__restrict__ x, const float *__restrict__ gate, int heads, int d, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256)
+        x[i] = from_f32<T>(to_f32<T>(x[i]) * gate[i / d]);          // i / d = t * heads + h
+}
+
+KESTREL_API int kestrel_head_scale(void *x, const float *gate, int dtype, int T, int heads, int d, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && heads > 0 && d > 0, "head_scale: bad sizes");
+    const size_t n = (size_t)T * heads * d;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    if (dtype == KESTREL_F32) kestrel_launch(head_scale_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float *)x, gate, heads, d, n);
+    else if (dtype == KESTREL_BF16) kestrel_launch(head_scale_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16 *)x, gate, heads, d, n);
+    else return kestrel_fail(-2, "head_scale: unknown dtype %d", dtype);
+    return kestrel_check_launch("head_scale");
 }
 
 // ---- head-wise products ------------------------------------------------------------------------

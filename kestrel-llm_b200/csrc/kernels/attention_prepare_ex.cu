@@ -3,7 +3,7 @@
 //
 // The product's columns are [ q: nq*hd | k: nkv*hd | v: nkv*vd | gate: nq ]; the k and v parts are
 // absent (`has_kv` = 0) in a layer that attends over another layer's cache, the gate part where
-// `gate_out` is null.  Per token:
+// `gate_out` is null, the q part where `nq` = 0 (keys and values alone, into pages).  Per token:
 //   every column gets its entry of `bias` (float32, indexed like the product's columns) if one is given;
 //   `qk_norm` = 1: q, k <- x / sqrt(mean(x^2) + eps) per head, times a weight [hd] where one is given;
 //   `qk_norm` = 2: the same over the whole q projection (all nq * hd columns at once) and the whole k
@@ -156,7 +156,7 @@ KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long lo
     KESTREL_REQUIRE(smem <= 40000, "attn_prepare_ex: %d heads exceed the shared memory of the norm over a whole projection", nq + nkv);
     const int keep_x = qk_norm == 2 && smem + (size_t)(nq + nkv) * hd * sizeof(float) <= 44 * 1024;
     if (keep_x) smem += (size_t)(nq + nkv) * hd * sizeof(float);
-    KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0 && vd > 0 && S > 0, "attn_prepare_ex: bad sizes");
+    KESTREL_REQUIRE(T > 0 && nq >= 0 && nkv > 0 && hd > 0 && vd > 0 && S > 0 && (nq > 0 || has_kv), "attn_prepare_ex: bad sizes");
     KESTREL_REQUIRE(hd <= 32 * APX_PER_LANE && vd <= 32 * APX_PER_LANE, "attn_prepare_ex: head size %d / %d exceeds %d", hd, vd, 32 * APX_PER_LANE);
     const int need = nq * hd + (has_kv ? nkv * (hd + vd) : 0) + (gate_out ? nq : 0);
     KESTREL_REQUIRE(ld >= need, "attn_prepare_ex: the product has %d columns, the heads need %d", ld, need);

@@ -962,11 +962,12 @@ def row_tiles(batch, rows_per_token: int, rows_per_tile: int = 256):
 
 def latent_prepare(fused: Partials, q_norm_w: torch.Tensor, kv_norm_w: torch.Tensor, norm_eps: float, positions: torch.Tensor,
                    seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, latent_cache: torch.Tensor, q_out: torch.Tensor,
-                   gate_out: Optional[torch.Tensor]) -> None:
+                   gate_out: Optional[torch.Tensor], kv_out: Optional[torch.Tensor] = None) -> None:
     """Columns [query latent | key/value latent | gate] of a fused product: both latents RMS-normed
     with their weights; the query latent to ``q_out`` [T, q_rank], the key/value latent into the
     token's slot of ``latent_cache`` [pages, 1, page size, kv_rank], sigmoid of the gate columns to
-    ``gate_out`` float32 [T, heads]."""
+    ``gate_out`` float32 [T, heads]; ``kv_out`` [T, kv_rank], if given, receives the step's key/value
+    latents as rows too."""
     _need(q_out, "latent_prepare.q_out", dims=2)
     _need(latent_cache, "latent_prepare.latent_cache", q_out.dtype, 4)
     _need(q_norm_w, "latent_prepare.q_norm_w", torch.float32, 1)
@@ -978,13 +979,27 @@ def latent_prepare(fused: Partials, q_norm_w: torch.Tensor, kv_norm_w: torch.Ten
     if gate_out is not None:
         _need(gate_out, "latent_prepare.gate_out", torch.float32, 2)
         n_gate = gate_out.shape[1]
+    if kv_out is not None:
+        _need(kv_out, "latent_prepare.kv_out", q_out.dtype, 2)
+        if kv_out.shape != (T, kv_rank):
+            raise KernelError("latent_prepare: kv_out has the wrong shape")
     if fused.tokens != T or fused.bias is not None or latent_cache.shape[1] != 1 or latent_cache.shape[2] != page_size or \
             q_norm_w.shape[0] != q_rank or kv_norm_w.shape[0] != kv_rank or (gate_out is not None and gate_out.shape[0] != T):
         raise KernelError("latent_prepare: shapes differ, or a bias is pending")
     _check(library().kestrel_latent_prepare(
         fused.data.data_ptr(), fused.slices, fused.slice_stride, fused.width, q_norm_w.data_ptr(), kv_norm_w.data_ptr(), float(norm_eps),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size), latent_cache.data_ptr(),
-        q_out.data_ptr(), _p(gate_out), _code(q_out, "latent_prepare.q_out"), T, q_rank, kv_rank, n_gate, _stream()))
+        q_out.data_ptr(), _p(gate_out), _p(kv_out), _code(q_out, "latent_prepare.q_out"), T, q_rank, kv_rank, n_gate, _stream()))
+
+
+def head_scale(x: torch.Tensor, gate: torch.Tensor, heads: int) -> None:
+    """x[t, h, :] *= gate[t, h] in place: x [T, heads * d], gate float32 [T, heads]."""
+    _need(x, "head_scale.x", dims=2)
+    _need(gate, "head_scale.gate", torch.float32, 2)
+    T = x.shape[0]
+    if gate.shape != (T, heads) or x.shape[1] % heads:
+        raise KernelError("head_scale: shapes differ")
+    _check(library().kestrel_head_scale(x.data_ptr(), gate.data_ptr(), _code(x, "head_scale.x"), T, heads, x.shape[1] // heads, _stream()))
 
 
 def head_gemm(x: torch.Tensor, w: torch.Tensor, heads: int, w_kn: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:

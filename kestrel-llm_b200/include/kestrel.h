@@ -188,8 +188,10 @@ KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, 
 KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w, const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
 
 /* ---- attention over cached latents (attention_latent.cu) ---- */
-/* product columns [q latent: q_rank | kv latent: kv_rank | gate: n_gate]: both latents RMS-normed with their weights; the query latent to q_out [T, q_rank], the kv latent into the token's slot of latent_cache [pages, 1, page_size, kv_rank], sigmoid of the gate columns to gate_out [T, n_gate] */
-KESTREL_API int kestrel_latent_prepare(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w, const float *kv_norm_w, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *latent_cache, void *q_out, float *gate_out, int dtype, int T, int q_rank, int kv_rank, int n_gate, kestrel_stream_t stream);
+/* product columns [q latent: q_rank | kv latent: kv_rank | gate: n_gate]: both latents RMS-normed with their weights; the query latent to q_out [T, q_rank], the kv latent into the token's slot of latent_cache [pages, 1, page_size, kv_rank], sigmoid of the gate columns to gate_out [T, n_gate]; kv_out (may be NULL) receives the kv latents as rows [T, kv_rank] too */
+KESTREL_API int kestrel_latent_prepare(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w, const float *kv_norm_w, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *latent_cache, void *q_out, float *gate_out, void *kv_out, int dtype, int T, int q_rank, int kv_rank, int n_gate, kestrel_stream_t stream);
+/* x[t, h, :] *= gate[t, h] in place, x [T, heads d] in the storage type */
+KESTREL_API int kestrel_head_scale(void *x, const float *gate, int dtype, int T, int heads, int d, kestrel_stream_t stream);
 /* out[t, h N + n] = sum_k x[t, h K + k] w_h[n, k]; w_kn = 0: w_h = rows [h N, (h + 1) N) of w [H N, K]; w_kn = 1: w_h[n, k] = w[h K + k, n] of w [H K, N]; all in the storage type, float32 sums */
 KESTREL_API int kestrel_head_gemm(const void *x, int ldx, const void *w, int ldw, int w_kn, void *out, int ldo, int dtype, int T, int H, int N, int K, kestrel_stream_t stream);
 KESTREL_API void kestrel_head_gemm_set_plain(int on);   /* 1: bfloat16 head-wise products take the CUDA-core kernel too; for tests of both */

@@ -15,6 +15,14 @@ attention runs over the cached latents themselves as ONE key/value head of size 
 all query heads (`PagedKVSpec.values_are_keys`): the queries are taken into the latent space by a
 head-wise product before it, the mixed latents out of it by another one afterwards.  W_dq, W_dkv
 and W_g are one fused product.  The gate may be absent (``head_gate=False``).
+
+One exception, for speed: a bfloat16 step in which every request STARTS (no request has tokens in
+the cache yet) and brings a long portion, with d = dv = 128.  All the keys its queries can see are
+then the step's own, so they are expanded once - k and v of the step's tokens from one fused product
+of their latents, into pages of a scratch cache - and the tcgen05 attention kernel runs over them
+with H key heads of 128 instead of one of ``kv_rank``; the gate follows as a kernel of its own.  The
+latents still go to the real cache, from which every later step reads.  The two forms differ by
+rounding only.
 """
 from __future__ import annotations
 
@@ -29,7 +37,10 @@ from .linear import Linear
 
 class LatentAttention(Mixer):
     force_plain = False        # tests: bfloat16 through the plain attention kernel too
-    graph_safe = True          # forward launches kernels over device tensors of the batch only
+    expand_prompts = True      # tests: off, starting portions too run over the cached latents
+    EXPAND_MIN_TOKENS = 64     # a step whose longest portion has more tokens may take the expanded form
+    graph_safe = True          # forward launches kernels over device tensors of the batch only (the expanded form reads the
+                               # host's copy of the step, and is never taken while a step is recorded)
 
     def __init__(self, width: int, heads: int, head_dim: int, v_head_dim: int, q_rank: int, kv_rank: int, dtype: torch.dtype, device,
                  prefix: str, scale: float, norm_eps: float, window: int = 0, head_gate: bool = True,
@@ -42,8 +53,9 @@ class LatentAttention(Mixer):
         self.prefix, self.names, self.dtype = prefix, names, dtype
         self.down = Linear(width, q_rank + kv_rank + (heads if head_gate else 0), dtype, device)
         self.up_q = Linear(q_rank, heads * head_dim, dtype, device)
-        self.up_k = Linear(kv_rank, heads * head_dim, dtype, device)       # used transposed, head by head
-        self.up_v = Linear(kv_rank, heads * v_head_dim, dtype, device)
+        self.up_kv = Linear(kv_rank, heads * (head_dim + v_head_dim), dtype, device)     # rows [k | v]: one product where both are expanded
+        self.up_k_w = self.up_kv.weight[:heads * head_dim]                  # used transposed, head by head
+        self.up_v_w = self.up_kv.weight[heads * head_dim:]
         self.out = Linear(heads * v_head_dim, width, dtype, device)
         self.q_norm_w = torch.empty((q_rank,), dtype=torch.float32, device=device)
         self.kv_norm_w = torch.empty((kv_rank,), dtype=torch.float32, device=device)
@@ -56,7 +68,7 @@ class LatentAttention(Mixer):
         w, r = self.down.weight, self.q_rank + self.kv_rank
         slots = [WeightSlot(p + dq, w[:self.q_rank]), WeightSlot(p + dkv, w[self.q_rank:r]),
                  WeightSlot(p + dq + ".norm", self.q_norm_w, "norm"), WeightSlot(p + dkv + ".norm", self.kv_norm_w, "norm"),
-                 WeightSlot(p + uq, self.up_q.weight), WeightSlot(p + uk, self.up_k.weight), WeightSlot(p + uv, self.up_v.weight),
+                 WeightSlot(p + uq, self.up_q.weight), WeightSlot(p + uk, self.up_k_w), WeightSlot(p + uv, self.up_v_w),
                  WeightSlot(p + o, self.out.weight)]
         if self.head_gate:
             slots.append(WeightSlot(p + g, w[r:]))
@@ -68,15 +80,48 @@ class LatentAttention(Mixer):
         cq = torch.empty((T, self.q_rank), dtype=self.dtype, device=x.device)
         gate = torch.empty((T, H), dtype=torch.float32, device=x.device) if self.head_gate else None
         table = batch.block_table(cache.group)
+        expand = (self.dtype == torch.bfloat16 and not self.force_plain and self.expand_prompts and self.head_dim == self.v_head_dim == 128
+                  and not batch.captured and batch.max_count > self.EXPAND_MIN_TOKENS and all(s == 0 for s in batch.starts)
+                  and ops.attention_tc_supported(128, cache.page_size))
+        c_rows = torch.empty((T, R), dtype=self.dtype, device=x.device) if expand else None
         ops.latent_prepare(fused, self.q_norm_w, self.kv_norm_w, self.norm_eps, batch.positions, batch.seq_of_token, table, cache.page_size,
-                           cache.k, cq, gate)
+                           cache.k, cq, gate, kv_out=c_rows)
         q = self.up_q.forward(cq).reduce(self.dtype)                           # [T, H d]
-        q_lat = ops.head_gemm(q, self.up_k.weight, H, w_kn=True)               # [T, H kv_rank]: Uk_n^T q_n
+        if expand:
+            return self._forward_expanded(q, c_rows, gate, batch, cache.page_size, residual)
+        q_lat = ops.head_gemm(q, self.up_k_w, H, w_kn=True)                    # [T, H kv_rank]: Uk_n^T q_n
         a = torch.empty((T, H * R), dtype=self.dtype, device=x.device)
         if self.dtype == torch.bfloat16 and not self.force_plain and ops.attention_window_supported(R, R, H, 1):
             ops.attention_window(q_lat, cache.k, cache.k, batch, table, cache.page_size, a, H, 1, R, R, self.window, 0, gate, self.scale)
         else:
             ops.attention_plain_ex(q_lat, cache.k, cache.k, batch.positions, batch.seq_of_token, table, cache.page_size, a, H, 1, R, R,
                                    self.window, 0, gate, self.scale)
-        o = ops.head_gemm(a, self.up_v.weight, H, w_kn=False)                  # [T, H dv]: Uv_n (mixed latent)
+        o = ops.head_gemm(a, self.up_v_w, H, w_kn=False)                       # [T, H dv]: Uv_n (mixed latent)
         return self.out.forward(o, residual=residual)      # many tokens: the product adds itself to the stream
+
+    def _forward_expanded(self, q, c_rows, gate, batch, page: int, residual):
+        """Starting portions: keys and values of the step's tokens expanded into scratch pages, tcgen05 attention over them."""
+        T, H, dev = q.shape[0], self.heads, q.device
+        kept = batch.__dict__.setdefault("_scratch_tables", {})
+        if page not in kept:         # every request's tokens from a page border, in the order of the step
+            blocks = [(n + page - 1) // page for n in batch.counts]
+            rows = torch.zeros((len(blocks), max(blocks)), dtype=torch.int32)
+            at = 0
+            for i, b in enumerate(blocks):
+                rows[i, :b] = torch.arange(at, at + b, dtype=torch.int32)
+                at += b
+            kept[page] = (rows.to(dev, non_blocking=True), at)
+        scratch_table, n_pages = kept[page]
+        k_pages = torch.empty((n_pages, H, page, 128), dtype=self.dtype, device=dev)
+        v_pages = torch.empty((n_pages, H, page, 128), dtype=self.dtype, device=dev)
+        kv = self.up_kv.forward(c_rows)                                        # columns [k: H d | v: H dv]
+        no_q = torch.empty((T, 0), dtype=self.dtype, device=dev)
+        ops.attn_prepare_ex(kv, None, None, None, self.norm_eps, batch.positions, batch.seq_of_token, scratch_table, page, k_pages, v_pages,
+                            no_q, None, 0, H, 128, 128, True)
+        a = torch.empty((T, H * 128), dtype=self.dtype, device=dev)
+        tile_seq, tile_row0 = ops.row_tiles(batch, 1, 256)
+        ops.attention_tc(q, k_pages, v_pages, a, tile_seq, tile_row0, batch.cu_seqlens, batch.kv_lens, scratch_table, page, H, H, 128,
+                         self.window, self.scale, rows_per_tile=256)
+        if gate is not None:
+            ops.head_scale(a, gate, H)
+        return self.out.forward(a, residual=residual)

@@ -279,6 +279,38 @@ def test_single_token_steps_share_their_keys_out_over_ctas(kind, sizes, size, n)
     assert np.abs(shared - one).max() <= 2e-2 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("sizes,size,page,cuts", [((4, 128, 128, 64, 96), 100, 16, [300, 2, 30] + [1] * 8), ((2, 128, 128, 40, 256), None, 32, [200]),
+                                                  ((5, 128, 128, 72, 40), 130, 8, [65, 70, 65]), ((3, 128, 128, 56, 72), 300, 64, [700])])
+def test_starting_portions_of_the_latent_mixer_expand_their_keys(sizes, size, page, cuts):
+    """bfloat16, d = dv = 128: a request's first portion (if long enough) runs the tcgen05 kernel over keys and values
+    expanded for the step, everything after it over the cached latents - against the plain statement and against the
+    same steps with the expanded form switched off; the latents the first portion left in the cache serve the later ones."""
+    from kestrel_llm_b200.csrc import ops
+    from kestrel_llm_b200.parts import LatentAttention
+    m = _m("latent_attention", sizes, 0.09, size)
+    n = sum(cuts)
+    calls = {"n": 0}
+    real = ops.attention_tc
+
+    def counted(*a, **kw):
+        calls["n"] += 1
+        return real(*a, **kw)
+    ops.attention_tc = counted
+    try:
+        fast, want, _ = _mixer_case("latent_attention", "bfloat16", m, page, n, cuts, seed=7, width=64)
+    finally:
+        ops.attention_tc = real
+    ops.raise_on_kernel_error()
+    assert calls["n"] == (1 if cuts[0] > LatentAttention.EXPAND_MIN_TOKENS else 0)
+    _close(fast, want, "bfloat16", "latent attention, first portion expanded")
+    LatentAttention.expand_prompts = False
+    try:
+        slow, _, _ = _mixer_case("latent_attention", "bfloat16", m, page, n, cuts, seed=7, width=64)
+    finally:
+        LatentAttention.expand_prompts = True
+    assert np.abs(fast - slow).max() <= 2e-2 * np.abs(want).max()
+
+
 @pytest.mark.parametrize("dtype,plain", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
 @pytest.mark.parametrize("T_,H,N,K", [(1, 3, 16, 24), (70, 4, 96, 64), (200, 2, 40, 136), (5, 1, 7, 5), (129, 20, 64, 16), (33, 2, 264, 72)])
 def test_head_wise_products(dtype, plain, T_, H, N, K):

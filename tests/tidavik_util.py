@@ -65,6 +65,7 @@ T3 = {"architecture": "Tidavik", "vocab": 131, "width": 64, "norm": {"eps": 1e-6
     layer(sink_attn(4, 2, 128, 128, 0.1, size=70, softcap=25.0), None),
     layer(latent(2, 32, 32, 48, 40, 0.2, size=200), 48),
     layer(sink_attn(2, 2, 128, 128, 0.08, size=260), 72),
+    layer(latent(3, 128, 128, 56, 72, 0.09, size=140), None),              # starting portions: keys and values expanded for the step
 ]}
 CONFIGS = {"T1": (T1, 3), "T2": (T2, 8), "T3": (T3, 5)}
 
