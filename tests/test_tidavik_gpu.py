@@ -311,6 +311,29 @@ def test_starting_portions_of_the_latent_mixer_expand_their_keys(sizes, size, pa
     assert np.abs(fast - slow).max() <= 2e-2 * np.abs(want).max()
 
 
+def test_requests_that_start_together_expand_their_keys_side_by_side():
+    """Three requests of unequal length start in one step (each from a page border of the scratch cache), then go on in
+    unequal portions and single tokens beside each other over the cached latents."""
+    rng = np.random.default_rng(12)
+    m = _m("latent_attention", (3, 128, 128, 48, 64), 0.09, 90)
+    mixer, W = _mixer_of("latent_attention", m, 64, "bfloat16", seed=3)
+    T.load_part(mixer, W)
+    Wr = T.bf16_round(W)
+    hs_in = [_rows(rng, n, 64) for n in (150, 97, 201)]
+    want = [P.MIXERS["latent_attention"](Wr, "l0.mix.", m, h, 1e-6) for h in hs_in]
+    hs = T.PartHarness(mixer, "bfloat16", max_tokens=640, page_size=16)
+    got = [[], [], []]
+    at = [0, 0, 0]
+    for cuts in [(100, 67, 131), (30, 2, 50), (1, 1, 1), (19, 27, 19)]:
+        out = hs.step([(i + 1, hs_in[i][at[i]:at[i] + c]) for i, c in enumerate(cuts)])
+        for i, c in enumerate(cuts):
+            got[i].append(out[i])
+            at[i] += c
+    assert at == [150, 97, 201]
+    for i in range(3):
+        _close(np.concatenate(got[i]), want[i], "bfloat16", f"latent attention, request {i} of three that started together")
+
+
 @pytest.mark.parametrize("dtype,plain", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
 @pytest.mark.parametrize("T_,H,N,K", [(1, 3, 16, 24), (70, 4, 96, 64), (200, 2, 40, 136), (5, 1, 7, 5), (129, 20, 64, 16), (33, 2, 264, 72)])
 def test_head_wise_products(dtype, plain, T_, H, N, K):
